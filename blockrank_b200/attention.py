@@ -1,0 +1,127 @@
+"""Drop-in registration of the CUDA BlockRank attention into Hugging Face transformers.
+
+Mirrors the reference's operator interface
+(src/blockrank/blockrank_std_attention.py:652-665 ``register_blockrank_attention`` and
+src/blockrank/blockrank_triton_kernel_attention.py:938-965
+``register_triton_blockrank_attention``): one call installs an attention
+function and a mask function under a name containing ``blockrank`` (the
+reference scripts switch to the block collator on that substring,
+scripts/eval_attn.py:36-38).
+
+Differences that matter to callers:
+  * the mask function returns compact block spans, an int32 ``(2, B, M)``
+    tensor (start, length per block), instead of the ``(B,1,M,H,H)`` additive
+    mask of std:264-309; an int32 ``(2, B, M)`` tensor passed as
+    ``attention_mask`` is taken as spans already (padding-free layout);
+  * K/V heads are shared inside the kernel (no ``repeat_kv`` copy) and the
+    output is written directly as ``(B, S, N, D)``;
+  * forward only: autograd through it raises NotImplementedError, like the
+    reference's Triton path (triton:759-761).
+"""
+from __future__ import annotations
+
+import warnings
+from typing import Optional
+
+import torch
+
+from . import _lib, ops
+
+ATTN_NAME = "cuda_blockrank"
+
+
+class BlockSpans(torch.Tensor):
+    """int32 (2, B, M) tensor [starts; lengths] that also carries ``max_block_len``."""
+
+    @staticmethod
+    def make(start: torch.Tensor, length: torch.Tensor, max_block_len: int) -> "BlockSpans":
+        t = torch.stack([start.to(torch.int32), length.to(torch.int32)]).contiguous().as_subclass(BlockSpans)
+        t.max_block_len = int(max_block_len)
+        return t
+
+
+def cuda_blockrank_attention_mask(*args, attention_mask: Optional[torch.Tensor] = None, **kwargs):
+    """Mask-interface entry.  Accepts both calling conventions of transformers (with or
+    without ``cache_position``; everything but ``attention_mask`` is ignored).
+
+    attention_mask: (B, M, H) bool/0-1 block mask from the block collator
+    (src/blockrank/dataset.py:228), or int32 (2, B, M) spans.
+    """
+    if attention_mask is None:
+        raise ValueError("cuda_blockrank attention needs the (B, M, H) block attention_mask of the block collator")
+    if isinstance(attention_mask, BlockSpans):
+        return attention_mask
+    if attention_mask.dim() != 3:
+        raise ValueError(f"expected a (B, M, H) block mask or (2, B, M) spans, got shape {tuple(attention_mask.shape)}")
+    if attention_mask.dtype == torch.int32 and attention_mask.shape[0] == 2:
+        mbl = kwargs.get("max_block_len")
+        if mbl is None:
+            mbl = int(attention_mask[1].max().item())
+        return BlockSpans.make(attention_mask[0], attention_mask[1], mbl)
+    start, length = ops.spans_from_mask(attention_mask)
+    return BlockSpans.make(start, length, attention_mask.shape[-1])
+
+
+def _wants_scores(module, kwargs) -> bool:
+    # same precedence as std:244-254
+    layers = kwargs.get("layers_to_return_scores", None)
+    if layers is not None:
+        idx = getattr(module, "layer_idx", None)
+        return idx is not None and idx in layers
+    return bool(kwargs.get("return_last_block_attn_scores", False))
+
+
+def cuda_blockrank_attention_forward(module, query, key, value, attention_mask, scaling: float,
+                                     dropout: float = 0.0, **kwargs):
+    """Attention-interface entry; same signature and return convention as
+    ``eager_blockrank_attention_forward`` (std:96-105).
+
+    query (B,N,S,D), key/value (B,Nk,S,D) -- the strided views HF produces are
+    consumed as they are.  Returns ``(attn_output (B,S,N,D), scores_or_None)``.
+    At layers selected by ``layers_to_return_scores`` /
+    ``return_last_block_attn_scores`` the second value is the raw logits of the
+    last ``num_last_queries`` slots, (B,N,R,S), exactly as the reference
+    returns them; with ``blockrank_doc_scores=True`` and ``signal_rows``
+    (B,R) slot indices it is instead the fused per-document probability mass
+    (B,N,R,num_docs).
+    """
+    if not isinstance(attention_mask, BlockSpans):
+        if attention_mask is None:
+            raise ValueError("BlockRank attention requires block spans (got attention_mask=None)")
+        attention_mask = cuda_blockrank_attention_mask(attention_mask=attention_mask, **kwargs)
+    if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
+        raise NotImplementedError("cuda_blockrank attention is forward-only; run under torch.no_grad()")
+    if dropout and getattr(module, "training", False):
+        warnings.warn("cuda_blockrank attention ignores attention dropout")
+    spans = attention_mask
+    start, length = spans[0], spans[1]
+    out = ops.attention(query, key, value, start, length, scaling, spans.max_block_len,
+                        algo=kwargs.get("blockrank_algo", _lib.ALGO_AUTO))
+    scores = None
+    if start.shape[-1] > 1 and _wants_scores(module, kwargs):
+        if kwargs.get("blockrank_doc_scores", False):
+            rows = kwargs.get("signal_rows")
+            if rows is None:
+                raise ValueError("blockrank_doc_scores=True needs signal_rows (B, R) slot indices")
+            scores, _ = ops.doc_scores(query, key, start, length, rows.to(device=query.device, dtype=torch.int32),
+                                       scaling, kwargs.get("temperature", 0.05))
+        else:
+            scores = ops.raw_scores(query, key, start, length, scaling, kwargs.get("num_last_queries", 16))
+    return out, scores
+
+
+def register_cuda_blockrank_attention(name: str = ATTN_NAME) -> str:
+    """Install the CUDA attention and its mask function in the transformers registries.
+
+    Idempotent.  Raises ImportError if libblockrank_b200.so has not been built
+    (the reference's Triton registration raises the same way when Triton is
+    missing, triton:953-957).  Select it with
+    ``model.set_attn_implementation(name)`` or ``attn_implementation=name``.
+    """
+    if "blockrank" not in name:
+        raise ValueError("the implementation name must contain 'blockrank'")
+    _lib.lib()  # fail now, not at the first forward
+    from transformers import AttentionInterface, AttentionMaskInterface
+    AttentionInterface.register(name, cuda_blockrank_attention_forward)
+    AttentionMaskInterface.register(name, cuda_blockrank_attention_mask)
+    return name

@@ -1,0 +1,162 @@
+// HBM-bound helpers of the early-exit runner: block spans from the collator
+// mask, RMSNorm (optionally fused with the residual add), rotate-half RoPE and
+// SiLU(gate) * up.  Rounding points follow what the HF Mistral modules do in
+// the model dtype, so a bf16 run tracks the framework's bf16 run closely.
+#include "brk_common.cuh"
+
+namespace brk {
+namespace {
+
+// ---- spans ------------------------------------------------------------------
+__global__ void spans_kernel(const uint8_t* __restrict__ mask, int total, int M, int H,
+                             int32_t* __restrict__ start, int32_t* __restrict__ len) {
+  // one warp per block: count valid slots; the block is left-padded so they are the last ones
+  const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (blk >= total) return;
+  const uint8_t* p = mask + (size_t)blk * H;
+  int c = 0;
+  for (int i = lane; i < H; i += 32) c += p[i] != 0;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
+  if (lane == 0) {
+    len[blk] = c;
+    start[blk] = (blk % M) * H + (H - c);
+  }
+}
+
+// ---- RMSNorm ------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                                                      const T* __restrict__ w, T* __restrict__ out, int hidden,
+                                                      float eps) {
+  extern __shared__ __align__(16) float row[];  // [hidden] the (summed) row in fp32
+  __shared__ float red[8];
+  const int64_t r = blockIdx.x;
+  const T* xp = x + r * hidden;
+  T* rp = residual ? residual + r * hidden : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float4 v = load4(xp + i);
+    if (rp) {
+      const float4 h = load4(rp + i);
+      // the framework adds in the model dtype: round the sum before it is normalised and stored
+      v = make_float4(Elem<T>::round(v.x + h.x), Elem<T>::round(v.y + h.y), Elem<T>::round(v.z + h.z),
+                      Elem<T>::round(v.w + h.w));
+      store4(rp + i, v);
+    }
+    *reinterpret_cast<float4*>(row + i) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+  const float rs = rsqrtf(tot / (float)hidden + eps);
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(row + i);
+    const float4 g = load4(w + i);
+    // normalised value is cast to the model dtype, then multiplied by the weight in that dtype
+    store4(out + r * hidden + i,
+           make_float4(g.x * Elem<T>::round(v.x * rs), g.y * Elem<T>::round(v.y * rs), g.z * Elem<T>::round(v.z * rs),
+                       g.w * Elem<T>::round(v.w * rs)));
+  }
+}
+
+// ---- RoPE ---------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ q, int64_t q_rs, int N, T* __restrict__ k, int64_t k_rs, int Nk, int D,
+                            const int32_t* __restrict__ pos, const float* __restrict__ inv_freq, int64_t T_rows) {
+  // one thread per (row, head, pair index i < D/2); heads of q then heads of k
+  const int half = D >> 1;
+  const int64_t per_row = (int64_t)(N + Nk) * half;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T_rows * per_row) return;
+  const int64_t t = idx / per_row;
+  const int rem = (int)(idx % per_row);
+  const int h = rem / half, i = rem % half;
+  T* base = h < N ? q + t * q_rs + (int64_t)h * D : k + t * k_rs + (int64_t)(h - N) * D;
+  const float ang = (float)pos[t] * inv_freq[i];
+  float sn, cs;
+  sincosf(ang, &sn, &cs);
+  cs = Elem<T>::round(cs);
+  sn = Elem<T>::round(sn);
+  const float x1 = Elem<T>::load(base + i), x2 = Elem<T>::load(base + i + half);
+  // x*cos + rotate_half(x)*sin with each product rounded in the model dtype
+  const float o1 = Elem<T>::round(x1 * cs) + Elem<T>::round(-x2 * sn);
+  const float o2 = Elem<T>::round(x2 * cs) + Elem<T>::round(x1 * sn);
+  Elem<T>::store(base + i, o1);
+  Elem<T>::store(base + i + half, o2);
+}
+
+// ---- SiLU(gate) * up ------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int inter) {
+  const int64_t per_row = inter / 4;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * per_row) return;
+  const int64_t r = idx / per_row;
+  const int c = (int)(idx % per_row) * 4;
+  const float4 g = load4(gu + r * 2 * inter + c);
+  const float4 u = load4(gu + r * 2 * inter + inter + c);
+  auto f = [](float x, float y) { return Elem<T>::round(x / (1.f + expf(-x))) * y; };
+  store4(out + r * inter + c, make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w)));
+}
+
+}  // namespace
+
+int spans_launch(const uint8_t* mask, int B, int M, int H, int32_t* start, int32_t* len, cudaStream_t st) {
+  const int total = B * M;
+  const int warps = 8;
+  spans_kernel<<<(total + warps - 1) / warps, warps * 32, 0, st>>>(mask, total, M, H, start, len);
+  BRK_CUDA(cudaGetLastError());
+  return BRK_OK;
+}
+
+int rmsnorm_launch(int dtype, const void* x, void* residual, const void* w, void* out, int64_t rows, int hidden,
+                   float eps, cudaStream_t st) {
+  const size_t sm = (size_t)hidden * 4;
+  if (dtype == BRK_BF16) {
+    if (sm > 48 * 1024)
+      BRK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, 256, sm, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)residual,
+                                                                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, hidden, eps);
+  } else {
+    if (sm > 48 * 1024)
+      BRK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    rmsnorm_kernel<float><<<(unsigned)rows, 256, sm, st>>>((const float*)x, (float*)residual, (const float*)w,
+                                                          (float*)out, hidden, eps);
+  }
+  BRK_CUDA(cudaGetLastError());
+  return BRK_OK;
+}
+
+int rope_launch(int dtype, void* q, int64_t q_rs, int N, void* k, int64_t k_rs, int Nk, int D, const int32_t* pos,
+                const float* inv_freq, int64_t T, cudaStream_t st) {
+  const int64_t total = T * (N + Nk) * (D / 2);
+  const int threads = 256;
+  const int64_t blocks = (total + threads - 1) / threads;
+  if (dtype == BRK_BF16)
+    rope_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, st>>>((__nv_bfloat16*)q, q_rs, N, (__nv_bfloat16*)k, k_rs,
+                                                                    Nk, D, pos, inv_freq, T);
+  else
+    rope_kernel<float><<<(unsigned)blocks, threads, 0, st>>>((float*)q, q_rs, N, (float*)k, k_rs, Nk, D, pos, inv_freq, T);
+  BRK_CUDA(cudaGetLastError());
+  return BRK_OK;
+}
+
+int silu_mul_launch(int dtype, const void* gu, void* out, int64_t rows, int inter, cudaStream_t st) {
+  const int64_t total = rows * (inter / 4);
+  const int threads = 256;
+  const int64_t blocks = (total + threads - 1) / threads;
+  if (dtype == BRK_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, inter);
+  else
+    silu_mul_kernel<float><<<(unsigned)blocks, threads, 0, st>>>((const float*)gu, (float*)out, rows, inter);
+  BRK_CUDA(cudaGetLastError());
+  return BRK_OK;
+}
+
+}  // namespace brk

@@ -1,0 +1,317 @@
+// Score extraction for BlockRank ranking: HBM-bound skinny products of a few
+// signal rows of Q against every document key.
+//
+//   doc_partial_kernel   one CTA per (document, prompt, KV head): each thread
+//                        owns whole key rows (read once per KV head, shared by
+//                        the G query heads of the group) and keeps an online
+//                        (max, sum-exp) per signal row; the CTA writes one
+//                        (max, sum) pair per (head, row, document).
+//   doc_finalize_kernel  one CTA per prompt: merges the per-document pairs
+//                        into the softmax over all document tokens, emits the
+//                        per-document probability mass and the mean/temperature
+//                        logits.
+//   raw_scores_kernel    compatibility output: raw masked logits of the last R
+//                        slots against every slot.
+#include "brk_common.cuh"
+
+namespace brk {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kRowBatch = 8;  // signal rows accumulated per pass over a key
+
+struct ScoreArgs {
+  View q, k;
+  const int32_t* rows;
+  const int32_t* blk_start;
+  const int32_t* blk_len;
+  float2* partial;  // [B, N, R, nd]
+  int B, N, Nk, S, M, R;
+  float scale;
+};
+
+__device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2) {
+  const float mn = fmaxf(m, m2);
+  const float ref = (mn == -INFINITY) ? 0.f : mn;
+  l = l * exp2f(m - ref) + l2 * exp2f(m2 - ref);
+  m = mn;
+}
+
+// dot products of one key row against kRowBatch staged query rows
+template <typename T, int D>
+__device__ __forceinline__ void key_dots(const T* __restrict__ kp, const float* __restrict__ qs, int nrows,
+                                         float (&acc)[kRowBatch]) {
+#pragma unroll
+  for (int i = 0; i < kRowBatch; ++i) acc[i] = 0.f;
+#pragma unroll 4
+  for (int d = 0; d < D; d += 4) {
+    const float4 kv = load4(kp + d);
+#pragma unroll
+    for (int i = 0; i < kRowBatch; ++i) {
+      if (i < nrows) {
+        const float4 qv = *reinterpret_cast<const float4*>(qs + i * D + d);
+        acc[i] = fmaf(qv.x, kv.x, acc[i]);
+        acc[i] = fmaf(qv.y, kv.y, acc[i]);
+        acc[i] = fmaf(qv.z, kv.z, acc[i]);
+        acc[i] = fmaf(qv.w, kv.w, acc[i]);
+      }
+    }
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  const int G = a.N / a.Nk;
+  const int GR = G * a.R;
+  float* qs = smem;                                    // [GR][D], scaled by scale*log2(e)
+  float2* red = reinterpret_cast<float2*>(qs + GR * D);  // [kThreads/32][kRowBatch]
+
+  const int nd = a.M - 2;
+  const int d = blockIdx.x;
+  const int b = blockIdx.y / a.Nk, g = blockIdx.y % a.Nk;
+  const int tid = threadIdx.x;
+  const int start = a.blk_start[(size_t)b * a.M + 1 + d];
+  const int len = a.blk_len[(size_t)b * a.M + 1 + d];
+
+  const float sl2 = a.scale * 1.4426950408889634f;
+  for (int i = tid; i < GR * (D / 4); i += kThreads) {
+    const int row = i / (D / 4), d4 = i % (D / 4);
+    const int hl = row / a.R, r = row % a.R;
+    const int slot = a.rows[b * a.R + r];
+    const T* qp = reinterpret_cast<const T*>(a.q.ptr) + (int64_t)b * a.q.sb + (int64_t)(g * G + hl) * a.q.sh +
+                  (int64_t)slot * a.q.ss;
+    float4 x = load4(qp + d4 * 4);
+    *reinterpret_cast<float4*>(qs + row * D + d4 * 4) = make_float4(x.x * sl2, x.y * sl2, x.z * sl2, x.w * sl2);
+  }
+  __syncthreads();
+
+  const T* kb = reinterpret_cast<const T*>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)g * a.k.sh;
+  for (int r0 = 0; r0 < GR; r0 += kRowBatch) {
+    const int nrows = min(kRowBatch, GR - r0);
+    float m[kRowBatch], l[kRowBatch];
+#pragma unroll
+    for (int i = 0; i < kRowBatch; ++i) { m[i] = -INFINITY; l[i] = 0.f; }
+    for (int t = tid; t < len; t += kThreads) {
+      float acc[kRowBatch];
+      key_dots<T, D>(kb + (int64_t)(start + t) * a.k.ss, qs + r0 * D, nrows, acc);
+#pragma unroll
+      for (int i = 0; i < kRowBatch; ++i)
+        if (i < nrows) merge_ml(m[i], l[i], acc[i], 1.f);
+    }
+    // warp then CTA reduction, fixed order
+#pragma unroll
+    for (int i = 0; i < kRowBatch; ++i) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m[i], off);
+        const float l2 = __shfl_xor_sync(0xffffffffu, l[i], off);
+        merge_ml(m[i], l[i], m2, l2);
+      }
+    }
+    __syncthreads();
+    if ((tid & 31) == 0) {
+#pragma unroll
+      for (int i = 0; i < kRowBatch; ++i) red[(tid >> 5) * kRowBatch + i] = make_float2(m[i], l[i]);
+    }
+    __syncthreads();
+    if (tid < nrows) {
+      float mm = -INFINITY, ll = 0.f;
+      for (int w = 0; w < kThreads / 32; ++w) {
+        const float2 x = red[w * kRowBatch + tid];
+        merge_ml(mm, ll, x.x, x.y);
+      }
+      const int row = r0 + tid;
+      const int n = g * G + row / a.R, r = row % a.R;
+      a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
+    }
+  }
+}
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* scratch) {
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float o = __shfl_xor_sync(0xffffffffu, v, off);
+    v = is_max ? fmaxf(v, o) : v + o;
+  }
+  __syncthreads();
+  if ((tid & 31) == 0) scratch[tid >> 5] = v;
+  __syncthreads();
+  float r = is_max ? -INFINITY : 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+  return r;
+}
+
+__global__ void __launch_bounds__(256) doc_finalize_kernel(const float2* __restrict__ partial, float* __restrict__ mass,
+                                                           float* __restrict__ logits, int NR, int nd,
+                                                           float inv_count_temp) {
+  extern __shared__ float acc[];  // [nd]
+  __shared__ float scratch[8];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  for (int d = tid; d < nd; d += blockDim.x) acc[d] = 0.f;
+  for (int nr = 0; nr < NR; ++nr) {
+    const float2* p = partial + ((size_t)b * NR + nr) * nd;
+    float mx = -INFINITY;
+    for (int d = tid; d < nd; d += blockDim.x) mx = fmaxf(mx, p[d].x);
+    mx = block_reduce(mx, true, scratch);
+    const float ref = (mx == -INFINITY) ? 0.f : mx;
+    float z = 0.f;
+    for (int d = tid; d < nd; d += blockDim.x) z += p[d].y * exp2f(p[d].x - ref);
+    z = block_reduce(z, false, scratch);
+    const float inv = z > 0.f ? 1.f / z : 0.f;
+    for (int d = tid; d < nd; d += blockDim.x) {
+      const float w = p[d].y * exp2f(p[d].x - ref) * inv;
+      mass[((size_t)b * NR + nr) * nd + d] = w;
+      acc[d] += w;  // each d is owned by one thread: deterministic
+    }
+  }
+  if (logits != nullptr)
+    for (int d = tid; d < nd; d += blockDim.x) logits[(size_t)b * nd + d] = acc[d] * inv_count_temp;
+}
+
+// block index of a slot, or -1 for padding (blk_start is non-decreasing)
+__device__ __forceinline__ int block_of(const int32_t* bs, const int32_t* bl, int M, int s) {
+  int lo = 0, hi = M;  // first index with bs > s
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (bs[mid] <= s) lo = mid + 1; else hi = mid;
+  }
+  const int m = lo - 1;
+  return (m >= 0 && s < bs[m] + bl[m]) ? m : -1;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads) raw_scores_kernel(ScoreArgs a, T* __restrict__ out, float neg) {
+  extern __shared__ __align__(16) float smem[];
+  const int G = a.N / a.Nk;
+  const int GR = G * a.R;
+  float* qs = smem;                               // [GR][D], scaled and rounded like the reference's Q*scaling
+  int* qblk = reinterpret_cast<int*>(qs + GR * D);  // [R] block index of each row (-1 = padding)
+  const int b = blockIdx.y / a.Nk, g = blockIdx.y % a.Nk;
+  const int tid = threadIdx.x;
+  const int32_t* bs = a.blk_start + (size_t)b * a.M;
+  const int32_t* bl = a.blk_len + (size_t)b * a.M;
+  for (int i = tid; i < GR * D; i += kThreads) {
+    const int row = i / D, dd = i % D;
+    const int hl = row / a.R, r = row % a.R;
+    const T* qp = reinterpret_cast<const T*>(a.q.ptr) + (int64_t)b * a.q.sb + (int64_t)(g * G + hl) * a.q.sh +
+                  (int64_t)(a.S - a.R + r) * a.q.ss;
+    qs[i] = Elem<T>::round(Elem<T>::load(qp + dd) * a.scale);
+  }
+  if (tid < a.R) qblk[tid] = block_of(bs, bl, a.M, a.S - a.R + tid);
+  __syncthreads();
+  const int s = blockIdx.x * kThreads + tid;
+  if (s >= a.S) return;
+  const int kblk = block_of(bs, bl, a.M, s);
+  const T* kp = reinterpret_cast<const T*>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)g * a.k.sh + (int64_t)s * a.k.ss;
+  for (int r0 = 0; r0 < GR; r0 += kRowBatch) {
+    const int nrows = min(kRowBatch, GR - r0);
+    float acc[kRowBatch];
+    key_dots<T, D>(kp, qs + r0 * D, nrows, acc);
+#pragma unroll
+    for (int i = 0; i < kRowBatch; ++i) {
+      if (i < nrows) {
+        const int row = r0 + i;
+        const int n = g * G + row / a.R, r = row % a.R;
+        const int qb = qblk[r], qslot = a.S - a.R + r;
+        const bool ok = qb >= 0 && kblk >= 0 &&
+                        ((kblk == qb && s <= qslot) || (qb == a.M - 1 && kblk < qb) ||
+                         (qb > 0 && qb < a.M - 1 && kblk == 0));
+        Elem<T>::store(out + (((size_t)b * a.N + n) * a.R + r) * a.S + s, ok ? acc[i] : neg);
+      }
+    }
+  }
+}
+
+ScoreArgs make_args(const brk_score_params& p) {
+  ScoreArgs a;
+  a.q = make_view(p.q);
+  a.k = make_view(p.k);
+  a.rows = p.rows;
+  a.blk_start = p.blk_start;
+  a.blk_len = p.blk_len;
+  a.partial = nullptr;
+  a.B = p.B; a.N = p.N; a.Nk = p.Nk; a.S = p.S; a.M = p.M; a.R = p.R;
+  a.scale = p.scale;
+  return a;
+}
+
+int check(const brk_score_params& p) {
+  BRK_REQUIRE(p.q.ptr && p.k.ptr && p.blk_start && p.blk_len, BRK_E_ARG, "null pointer in score params");
+  BRK_REQUIRE(p.B > 0 && p.N > 0 && p.Nk > 0 && p.N % p.Nk == 0 && p.S > 0 && p.M >= 1, BRK_E_ARG,
+              "bad score shape B=%d N=%d Nk=%d S=%d M=%d", p.B, p.N, p.Nk, p.S, p.M);
+  BRK_REQUIRE(p.R >= 1 && p.R <= 64 && (p.N / p.Nk) * p.R <= 256, BRK_E_ARG, "R=%d out of range", p.R);
+  BRK_REQUIRE(p.D == 64 || p.D == 128, BRK_E_UNSUPPORTED, "head_dim %d not supported (64 or 128)", p.D);
+  BRK_REQUIRE(p.dtype == BRK_BF16 || p.dtype == BRK_F32, BRK_E_UNSUPPORTED, "dtype %d", p.dtype);
+  const int al = p.dtype == BRK_BF16 ? 8 : 4;
+  BRK_REQUIRE(p.q.stride_s % al == 0 && p.q.stride_h % al == 0 && p.q.stride_b % al == 0 && p.k.stride_s % al == 0 &&
+                  p.k.stride_h % al == 0 && p.k.stride_b % al == 0 && ((uintptr_t)p.q.ptr % 16 == 0) &&
+                  ((uintptr_t)p.k.ptr % 16 == 0),
+              BRK_E_ARG, "q/k rows must be 16-byte aligned");
+  BRK_REQUIRE(p.B * p.Nk <= 65535, BRK_E_UNSUPPORTED, "B*Nk too large");
+  return BRK_OK;
+}
+
+}  // namespace
+
+size_t doc_scores_workspace(const brk_score_params& p) {
+  const size_t nd = p.M > 2 ? p.M - 2 : 0;
+  return (size_t)p.B * p.N * p.R * nd * sizeof(float2);
+}
+
+int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
+  int rc = check(p);
+  if (rc) return rc;
+  BRK_REQUIRE(p.M >= 3, BRK_E_ARG, "document scores need at least one document block (M=%d)", p.M);
+  BRK_REQUIRE(p.rows && p.doc_mass, BRK_E_ARG, "rows / doc_mass must be given");
+  BRK_REQUIRE(ws != nullptr && ws_bytes >= doc_scores_workspace(p), BRK_E_WORKSPACE, "workspace %zu < %zu bytes",
+              ws_bytes, doc_scores_workspace(p));
+  BRK_REQUIRE(p.temperature > 0.f, BRK_E_ARG, "temperature must be positive");
+  ScoreArgs a = make_args(p);
+  a.partial = reinterpret_cast<float2*>(ws);
+  const int nd = p.M - 2, G = p.N / p.Nk;
+  dim3 grid(nd, p.B * p.Nk);
+  const size_t sm = (size_t)G * p.R * p.D * 4 + (kThreads / 32) * kRowBatch * sizeof(float2);
+  auto launch = [&](auto kern) -> int {
+    if (sm > 48 * 1024) BRK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    kern<<<grid, kThreads, sm, st>>>(a);
+    BRK_CUDA(cudaGetLastError());
+    return BRK_OK;
+  };
+  if (p.dtype == BRK_BF16) rc = p.D == 128 ? launch(doc_partial_kernel<__nv_bfloat16, 128>) : launch(doc_partial_kernel<__nv_bfloat16, 64>);
+  else rc = p.D == 128 ? launch(doc_partial_kernel<float, 128>) : launch(doc_partial_kernel<float, 64>);
+  if (rc) return rc;
+  doc_finalize_kernel<<<p.B, 256, (size_t)nd * 4, st>>>(a.partial, p.doc_mass, p.logits, p.N * p.R, nd,
+                                                        1.f / ((float)(p.N * p.R) * p.temperature));
+  BRK_CUDA(cudaGetLastError());
+  return BRK_OK;
+}
+
+int raw_scores_launch(const brk_score_params& p, void* out, cudaStream_t st) {
+  int rc = check(p);
+  if (rc) return rc;
+  BRK_REQUIRE(out != nullptr, BRK_E_ARG, "out is null");
+  BRK_REQUIRE(p.R <= p.S, BRK_E_ARG, "R=%d exceeds S=%d", p.R, p.S);
+  ScoreArgs a = make_args(p);
+  const int G = p.N / p.Nk;
+  dim3 grid((p.S + kThreads - 1) / kThreads, p.B * p.Nk);
+  const size_t sm = (size_t)G * p.R * p.D * 4 + p.R * sizeof(int);
+  auto launch = [&](auto kern, auto* o, float neg) -> int {
+    if (sm > 48 * 1024) BRK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    kern<<<grid, kThreads, sm, st>>>(a, o, neg);
+    BRK_CUDA(cudaGetLastError());
+    return BRK_OK;
+  };
+  // 0.7 * lowest finite value of the dtype, computed the way the reference does (python float -> dtype)
+  if (p.dtype == BRK_BF16) {
+    const float neg = 0.7f * -3.3895313892515355e38f;
+    return p.D == 128 ? launch(raw_scores_kernel<__nv_bfloat16, 128>, (__nv_bfloat16*)out, neg)
+                      : launch(raw_scores_kernel<__nv_bfloat16, 64>, (__nv_bfloat16*)out, neg);
+  }
+  const float neg = (float)(0.7 * -3.4028234663852886e38);
+  return p.D == 128 ? launch(raw_scores_kernel<float, 128>, (float*)out, neg)
+                    : launch(raw_scores_kernel<float, 64>, (float*)out, neg);
+}
+
+}  // namespace brk

@@ -1,0 +1,206 @@
+"""Early-exit Mistral-architecture prefill ranker: what scripts/eval_attn.py does, minus the waste.
+
+The reference scores documents by running the HF model with every layer after
+the scoring layer ``l*`` patched to identity (scripts/eval_attn.py:121-130) and
+reducing that layer's raw attention logits (src/blockrank/losses.py:37-78).
+Layer ``l*`` itself still runs completely there.  This runner computes the same
+scores with the minimal work: layers 0..l*-1 in full, and at layer ``l*`` only
+the input RMSNorm, ``k_proj`` for every token, ``q_proj`` for the signal rows,
+RoPE and the fused score epilogue.
+
+Dense projections are cuBLAS GEMMs through torch.matmul; RMSNorm, RoPE,
+SiLU*up, the block-sparse attention and the scorer are this package's CUDA
+kernels.  Weights use the HF parameter names, so a real checkpoint's state
+dict loads directly.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+from . import ops, _lib
+
+
+@dataclass
+class RankerConfig:
+    vocab_size: int = 32768
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    rope_theta: float = 1e6
+    rms_norm_eps: float = 1e-5
+    score_layer: int = 20
+    temperature: float = 0.05
+
+    @staticmethod
+    def mistral_7b(score_layer: int = 20) -> "RankerConfig":
+        return RankerConfig(score_layer=score_layer)
+
+    @staticmethod
+    def tiny(score_layer: int = 2) -> "RankerConfig":
+        return RankerConfig(vocab_size=32768, hidden_size=256, intermediate_size=688, num_hidden_layers=4,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=64, score_layer=score_layer)
+
+
+class MistralPrefillRanker:
+    """Holds the fused weights of layers 0..score_layer on one GPU and ranks prompts."""
+
+    def __init__(self, cfg: RankerConfig, device, dtype=torch.bfloat16):
+        if cfg.score_layer >= cfg.num_hidden_layers:
+            raise ValueError("score_layer must index an existing layer")
+        _lib.lib()  # no CUDA library, no runner
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.embed: Optional[torch.Tensor] = None
+        self.layers = []  # dicts: ln1, wqkv, wo, ln2, wgu, wd   (scoring layer: ln1, wq, wk)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.int64).float() / cfg.head_dim))
+        self.inv_freq = inv.to(self.device)
+        self.algo = _lib.ALGO_AUTO
+        self.events = None  # set to {"attn": [], "score": []} to collect (start, end) CUDA events per launch
+
+    # ---- weights ---------------------------------------------------------------
+    def load_state_dict(self, sd: Dict[str, torch.Tensor]) -> "MistralPrefillRanker":
+        """Take HF-named tensors (model.embed_tokens.weight, model.layers.{i}.self_attn.q_proj.weight, ...)."""
+        c, dev, dt = self.cfg, self.device, self.dtype
+        g = lambda name: sd[name].detach().to(device=dev, dtype=dt)
+        self.embed = g("model.embed_tokens.weight")
+        self.layers = []
+        for i in range(c.score_layer + 1):
+            p = f"model.layers.{i}."
+            L = {"ln1": g(p + "input_layernorm.weight")}
+            if i < c.score_layer:
+                L["wqkv"] = torch.cat([g(p + "self_attn.q_proj.weight"), g(p + "self_attn.k_proj.weight"),
+                                       g(p + "self_attn.v_proj.weight")], 0).contiguous()
+                L["wo"] = g(p + "self_attn.o_proj.weight")
+                L["ln2"] = g(p + "post_attention_layernorm.weight")
+                L["wgu"] = torch.cat([g(p + "mlp.gate_proj.weight"), g(p + "mlp.up_proj.weight")], 0).contiguous()
+                L["wd"] = g(p + "mlp.down_proj.weight")
+            else:
+                L["wq"] = g(p + "self_attn.q_proj.weight")
+                L["wk"] = g(p + "self_attn.k_proj.weight")
+            self.layers.append(L)
+        return self
+
+    def init_random(self, seed: int = 3, std: float = 0.02) -> "MistralPrefillRanker":
+        """Random weights N(0, std) drawn on the device (norm weights 1); only layers 0..score_layer exist."""
+        c, dev, dt = self.cfg, self.device, self.dtype
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        rnd = lambda *shape: (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * std).to(dt)
+        ones = lambda n: torch.ones(n, device=dev, dtype=dt)
+        qd, kd = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+        self.embed = rnd(c.vocab_size, c.hidden_size)
+        self.layers = []
+        for i in range(c.score_layer + 1):
+            L = {"ln1": ones(c.hidden_size)}
+            if i < c.score_layer:
+                L["wqkv"] = rnd(qd + 2 * kd, c.hidden_size)
+                L["wo"] = rnd(c.hidden_size, qd)
+                L["ln2"] = ones(c.hidden_size)
+                L["wgu"] = rnd(2 * c.intermediate_size, c.hidden_size)
+                L["wd"] = rnd(c.hidden_size, c.intermediate_size)
+            else:
+                L["wq"] = rnd(qd, c.hidden_size)
+                L["wk"] = rnd(kd, c.hidden_size)
+            self.layers.append(L)
+        return self
+
+    # ---- forward ---------------------------------------------------------------
+    @torch.no_grad()
+    def hidden_before_score_layer(self, input_ids, position_ids, blk_start, blk_len, max_block_len):
+        """Run layers 0..l*-1; returns (residual stream h, pending branch output d) so that the
+        scoring layer can fuse the last residual add with its RMSNorm.  Shapes (B*S, hidden)."""
+        c = self.cfg
+        B, S = input_ids.shape
+        N, Nk, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        qd, kd = N * D, Nk * D
+        T = B * S
+        pos = position_ids.reshape(T).to(torch.int32)
+        h = torch.embedding(self.embed, input_ids.reshape(T))
+        scale = D ** -0.5
+        pending = None  # MLP output not yet added to h
+        for i in range(c.score_layer):
+            L = self.layers[i]
+            x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps) if pending is None else \
+                ops.rmsnorm(pending, L["ln1"], c.rms_norm_eps, residual=h)
+            qkv = torch.matmul(x, L["wqkv"].t())                         # (T, qd + 2 kd)
+            q3 = qkv[:, :qd].view(T, N, D)
+            k3 = qkv[:, qd:qd + kd].view(T, Nk, D)
+            ops.rope_(q3, k3, pos, self.inv_freq)
+            q4 = qkv[:, :qd].view(B, S, N, D).permute(0, 2, 1, 3)
+            k4 = qkv[:, qd:qd + kd].view(B, S, Nk, D).permute(0, 2, 1, 3)
+            v4 = qkv[:, qd + kd:].view(B, S, Nk, D).permute(0, 2, 1, 3)
+            ev = self._tick("attn")
+            attn = ops.attention(q4, k4, v4, blk_start, blk_len, scale, max_block_len, algo=self.algo)
+            self._tock(ev)
+            o = torch.matmul(attn.view(T, qd), L["wo"].t())
+            x = ops.rmsnorm(o, L["ln2"], c.rms_norm_eps, residual=h)    # h += o
+            act = ops.silu_mul(torch.matmul(x, L["wgu"].t()))
+            pending = torch.matmul(act, L["wd"].t())
+        return h, pending
+
+    @torch.no_grad()
+    def score(self, input_ids, position_ids, blk_start, blk_len, max_block_len, signal_rows):
+        """input_ids/position_ids (B, S) on the device, spans int32 (B, M), signal_rows int32 (B, R).
+
+        Returns (logits (B, num_docs) fp32, doc_mass (B, N, R, num_docs) fp32).
+        """
+        c = self.cfg
+        B, S = input_ids.shape
+        N, Nk, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        R = signal_rows.shape[1]
+        h, pending = self.hidden_before_score_layer(input_ids, position_ids, blk_start, blk_len, max_block_len)
+        L = self.layers[c.score_layer]
+        x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps) if pending is None else \
+            ops.rmsnorm(pending, L["ln1"], c.rms_norm_eps, residual=h)
+        T = B * S
+        pos = position_ids.reshape(T).to(torch.int32)
+        k = torch.matmul(x, L["wk"].t()).view(T, Nk, D)
+        flat_rows = (signal_rows.to(torch.int64) + torch.arange(B, device=x.device)[:, None] * S).reshape(-1)
+        q = torch.matmul(x.index_select(0, flat_rows), L["wq"].t()).view(B * R, N, D)
+        # RoPE: keys of every token, queries of the signal rows only
+        ops.rope_(q, None, pos.index_select(0, flat_rows), self.inv_freq)
+        ops.rope_(None, k, pos, self.inv_freq)
+        q4 = q.view(B, R, N, D).permute(0, 2, 1, 3)
+        k4 = k.view(B, S, Nk, D).permute(0, 2, 1, 3)
+        local_rows = torch.arange(R, device=x.device, dtype=torch.int32).expand(B, R).contiguous()
+        ev = self._tick("score")
+        mass, logits = ops.doc_scores(q4, k4, blk_start, blk_len, local_rows, D ** -0.5, c.temperature)
+        self._tock(ev)
+        return logits, mass
+
+    def _tick(self, kind):
+        if self.events is None:
+            return None
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.events[kind].append((a, b))
+        a.record()
+        return b
+
+    @staticmethod
+    def _tock(ev):
+        if ev is not None:
+            ev.record()
+
+    @torch.no_grad()
+    def rank_host(self, batch: dict, k: int = 10):
+        """End-to-end call on HOST tensors: ``batch`` holds pinned ``input_ids``/``position_ids`` (B, S) int64,
+        ``block_spans`` int32 (2, B, M), ``signal_rows`` int32 (B, R) and ``max_block_len``.  Copies them to the
+        device, scores, and returns (logits, top-k document indices) on the host."""
+        dev = self.device
+        ids = batch["input_ids"].to(dev, non_blocking=True)
+        pos = batch["position_ids"].to(dev, non_blocking=True)
+        spans = batch["block_spans"].to(dev, non_blocking=True)
+        rows = batch["signal_rows"].to(dev, non_blocking=True)
+        logits, _ = self.score(ids, pos, spans[0], spans[1], int(batch["max_block_len"]), rows)
+        top = torch.topk(logits, k=min(k, logits.shape[-1]), dim=-1).indices
+        return logits.cpu(), top.cpu()
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * self.embed.element_size()
+        for L in self.layers:
+            n += sum(t.numel() * t.element_size() for t in L.values())
+        return n

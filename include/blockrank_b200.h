@@ -1,0 +1,157 @@
+/*
+ * blockrank_b200 -- C ABI of the B200 (sm_100a) BlockRank prefill kernels.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers, sizes and strides,
+ * never allocates or frees device memory, and is asynchronous on the CUDA
+ * stream it is given (a `cudaStream_t` passed as `void*`).  Functions return
+ * 0 on success and a negative BRK_E_* code on failure; brk_last_error() gives
+ * the message of the calling thread's last failure.
+ *
+ * Vocabulary.  A prompt is a sequence of S token slots split into M blocks:
+ * block 0 is the instruction prefix, blocks 1..M-2 are documents, block M-1 is
+ * the query block (M == 1: a single causal block; M == 2: prefix + query).
+ * Block m of prompt b occupies slots [blk_start[b*M+m], +blk_len[b*M+m]);
+ * blocks are ordered and do not overlap; slots outside every block are
+ * padding.  This covers both the reference's left-padded (B, M, H) grid and a
+ * padding-free packed layout.  Allowed (query, key) pairs -- the pattern of
+ * src/blockrank/blockrank_std_attention.py:158-237 in the reference:
+ *   same block and key slot <= query slot;
+ *   query in a document block and key in block 0;
+ *   query in the last block and key in any earlier block.
+ *
+ * Tensors are addressed as ptr[b*stride_b + s*stride_s + h*stride_h + d] in
+ * elements (innermost stride 1), so the HF layout [B, S, heads, D] viewed as
+ * (B, heads, S, D) is passed without a copy, and grouped-query K/V heads are
+ * shared inside the kernels (no repeat_kv copy).
+ */
+#ifndef BLOCKRANK_B200_H_
+#define BLOCKRANK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BRK_VERSION 100
+
+#if defined(__GNUC__)
+#define BRK_API __attribute__((visibility("default")))
+#else
+#define BRK_API
+#endif
+
+enum {
+  BRK_OK = 0,
+  BRK_E_ARG = -1,        /* bad shape / stride / alignment / null pointer */
+  BRK_E_UNSUPPORTED = -2,/* head_dim, dtype or algorithm not available */
+  BRK_E_WORKSPACE = -3,  /* workspace too small */
+  BRK_E_CUDA = -4,       /* a CUDA call failed (launch, attribute, tensor map) */
+  BRK_E_DEVICE = -5,     /* device is not sm_100 */
+  BRK_E_TIMEOUT = -6     /* a bounded device-side wait gave up (status word set) */
+};
+
+enum { BRK_BF16 = 0, BRK_F32 = 1 };
+
+/* attention algorithm selector */
+enum {
+  BRK_ALGO_AUTO = 0,  /* tcgen05 kernel for bf16 / head_dim 128, otherwise SIMT */
+  BRK_ALGO_SIMT = 1,  /* CUDA-core fp32-accumulate kernel: bf16 and fp32, head_dim 64 or 128 */
+  BRK_ALGO_TC = 2     /* tcgen05 + TMEM + TMA kernel: bf16, head_dim 128 */
+};
+
+/* A (B, heads, S, D) tensor view; strides in elements, innermost stride 1. */
+typedef struct brk_view {
+  void* ptr;
+  int64_t stride_b;
+  int64_t stride_h;
+  int64_t stride_s;
+} brk_view;
+
+/* Replaces the attention call made by the registered attention functions
+ * (reference: eager_blockrank_attention_forward,
+ * src/blockrank/blockrank_std_attention.py:96-262, and
+ * kernelized_blockrank_attention_forward_with_full_mask,
+ * src/blockrank/blockrank_triton_kernel_attention.py:609-746). */
+typedef struct brk_attn_params {
+  int32_t dtype;          /* BRK_BF16 or BRK_F32 (q, k, v, o share it) */
+  int32_t algo;           /* BRK_ALGO_* */
+  int32_t B, N, Nk, D;    /* prompts, query heads, KV heads, head dim */
+  int32_t S;              /* token slots per prompt */
+  int32_t M;              /* blocks per prompt */
+  int32_t max_block_len;  /* upper bound on blk_len (sizes the grid) */
+  float scale;            /* softmax scale (the model's `scaling`) */
+  brk_view q, k, v, o;    /* o is written as [B, S, N, D] through its strides */
+  float* lse;             /* optional [B, N, S] natural-log sum-exp of scaled logits; NULL to skip */
+  const int32_t* blk_start; /* device, [B*M] */
+  const int32_t* blk_len;   /* device, [B*M] */
+  int32_t* status;        /* optional device word; set non-zero if a bounded wait gave up */
+} brk_attn_params;
+
+BRK_API int brk_version(void);
+BRK_API const char* brk_last_error(void);
+/* 0 if the current device is sm_100, BRK_E_DEVICE otherwise. */
+BRK_API int brk_device_check(void);
+
+/* Block spans from the collator's left-padded (B, M, H) boolean mask (one byte
+ * per slot).  Replaces the (B,1,M,H,H) additive mask built by
+ * eager_blockrank_attention_mask (src/blockrank/blockrank_std_attention.py:264-309):
+ * the kernels need only start/length per block. */
+BRK_API int brk_spans_from_mask(const uint8_t* mask, int32_t B, int32_t M, int32_t H,
+                        int32_t* blk_start, int32_t* blk_len, void* stream);
+
+BRK_API size_t brk_attn_fwd_workspace_bytes(const brk_attn_params* p);
+BRK_API int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Fused score epilogue.  Replaces _compute_last_block_scores_kernel +
+ * compute_last_block_attention_scores
+ * (src/blockrank/blockrank_triton_kernel_attention.py:432-606) followed by
+ * compute_auxiliary_attention_loss(..., return_logits=True)
+ * (src/blockrank/losses.py:37-78): for each signal row the softmax over all
+ * valid document tokens is summed per document, without materialising the
+ * (B, N, R, S) logit slab.
+ *   rows      device [B*R] slot indices of the signal rows (inside the query block)
+ *   doc_mass  device [B, N, R, M-2] fp32 out: per head / row normalised mass per document
+ *   logits    device [B, M-2] fp32 out, optional: mean over heads and rows / temperature
+ * workspace: brk_doc_scores_workspace_bytes() bytes of device scratch. */
+typedef struct brk_score_params {
+  int32_t dtype;
+  int32_t B, N, Nk, D, S, M, R;
+  float scale;
+  float temperature;
+  brk_view q, k;
+  const int32_t* rows;
+  const int32_t* blk_start;
+  const int32_t* blk_len;
+  float* doc_mass;
+  float* logits;
+} brk_score_params;
+
+BRK_API size_t brk_doc_scores_workspace_bytes(const brk_score_params* p);
+BRK_API int brk_doc_scores(const brk_score_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Compatibility output of the reference's second return value: raw scaled,
+ * masked logits of the last R slots of the prompt against every slot,
+ * out[B, N, R, S] in `dtype`, masked entries = 0.7 * lowest finite value of the
+ * dtype (src/blockrank/blockrank_std_attention.py:233, :256-262, :306).
+ * Uses q, k, scale, blk_* of brk_score_params; rows/doc_mass/logits ignored. */
+BRK_API int brk_raw_scores(const brk_score_params* p, void* out, void* stream);
+
+/* Runner helpers (the model code around the attention call; the reference
+ * relies on transformers' modeling_mistral.py for these). All row-major. */
+/* out = weight * (x * rsqrt(mean(x^2) + eps)); if residual != NULL first
+ * residual += x (stored) and the norm is taken of the sum. */
+BRK_API int brk_rmsnorm(int32_t dtype, const void* x, void* residual, const void* weight, void* out,
+                int64_t rows, int32_t hidden, float eps, void* stream);
+/* In-place rotate-half RoPE on q [T, N, D] and k [T, Nk, D] (row stride given
+ * in elements), angle = pos[t] * inv_freq[i].  q may be NULL when N == 0, k when Nk == 0. */
+BRK_API int brk_rope(int32_t dtype, void* q, int64_t q_row_stride, int32_t N, void* k, int64_t k_row_stride,
+             int32_t Nk, int32_t D, const int32_t* pos, const float* inv_freq, int64_t T, void* stream);
+/* out[r, c] = silu(gate_up[r, c]) * gate_up[r, inter + c]. */
+BRK_API int brk_silu_mul(int32_t dtype, const void* gate_up, void* out, int64_t rows, int32_t inter, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLOCKRANK_B200_H_ */
