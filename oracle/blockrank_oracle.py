@@ -319,11 +319,11 @@ def mistral_prefill_scores(w: dict, cfg: dict, input_ids, position_ids, mask_bmh
         x = rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_eps"])
         q = (x @ w[p + "self_attn.q_proj.weight"].T).view(B, S, N, D).transpose(1, 2)
         k = (x @ w[p + "self_attn.k_proj.weight"].T).view(B, S, Nk, D).transpose(1, 2)
-        v = (x @ w[p + "self_attn.v_proj.weight"].T).view(B, S, Nk, D).transpose(1, 2)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-        if i == score_layer:
+        if i == score_layer:  # only the logits of this layer are needed (V, o_proj and the MLP are not)
             raw = raw_last_scores(q, k, mask_bmh, scaling, num_last)
             break
+        v = (x @ w[p + "self_attn.v_proj.weight"].T).view(B, S, Nk, D).transpose(1, 2)
         a = attention_blocked(q, k, v, mask_bmh, scaling).to(h.dtype)
         h = h + a.reshape(B, S, N * D) @ w[p + "self_attn.o_proj.weight"].T
         x = rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["rms_eps"])
