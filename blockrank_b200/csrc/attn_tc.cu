@@ -87,6 +87,10 @@ struct TcArgs {
   int B, N, Nk, S, M;
   int G, g_shift;  // query heads per KV head, log2
   float scale_log2;
+  int n_split;     // key chunks the query block's context is cut into (1 = no split)
+  int lq_max;      // rows per (prompt, head) in the partial buffers (= max_block_len)
+  float* part_o;   // [B, N, lq_max, n_split, 128] un-normalised partial outputs
+  float2* part_ml; // [B, N, lq_max, n_split] (running max in log2 units, sum)
 };
 
 enum { kBarQ = 0, kBarK0 = 1, kBarK1 = 2, kBarV0 = 3, kBarV1 = 4, kBarS0 = 5, kBarS1 = 6, kBarO = 7, kNumBars = 8 };
@@ -109,7 +113,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z / a.Nk, g = blockIdx.z % a.Nk;
-  const int m = a.M - 1 - blockIdx.y;  // long query-block CTAs first
+  // grid.y: first the n_split key chunks of the query block (longest work first), then blocks M-2 .. 0
+  const bool is_last = (int)blockIdx.y < a.n_split;
+  const int chunk = is_last ? (int)blockIdx.y : 0;
+  const int m = is_last ? a.M - 1 : a.M - 2 - ((int)blockIdx.y - a.n_split);
   const int tile = blockIdx.x;
   const int G = a.G, TOK = BM >> a.g_shift;
   const int32_t* bs = a.blk_start + (size_t)b * a.M;
@@ -117,7 +124,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int start = bs[m], len = bl[m];
 
   __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.sb;
-  if (tile == 0) {
+  if (tile == 0 && chunk == 0) {
     // padding slots in front of this block (and behind the last one) are written as zeros
     const int gap0 = (m == 0) ? 0 : bs[m - 1] + bl[m - 1];
     const int per_row = G * (HD / 8);
@@ -164,7 +171,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
   const int own_n = min(len, t0 + TOK);
   const int n_ctx = (ctx_hi - ctx_lo + BN - 1) / BN;
-  const int n_tiles = n_ctx + (own_n + BN - 1) / BN;
+  // this CTA's share of the tile list: everything, or one chunk of the context (+ own keys for the last chunk)
+  int j0 = 0, n_tiles = n_ctx + (own_n + BN - 1) / BN;
+  const bool split = is_last && a.n_split > 1;
+  if (split) {
+    const int per = (n_ctx + a.n_split - 1) / a.n_split;
+    j0 = min(n_ctx, chunk * per);
+    const int j1 = (chunk == a.n_split - 1) ? n_tiles : min(n_ctx, j0 + per);
+    n_tiles = j1 - j0;
+    if (n_tiles <= 0) {  // empty chunk: leave a neutral partial for the combine step
+      const int rr = tid, rtok = t0 + (rr >> a.g_shift);
+      if (rtok < len && rtok < a.lq_max)
+        a.part_ml[(((int64_t)b * a.N + g * G + (rr & (G - 1))) * a.lq_max + rtok) * a.n_split + chunk] =
+            make_float2(-INFINITY, 0.f);
+      return;
+    }
+  }
 
   bool failed = (sbase - raw) > 512u;  // cannot happen with the 1024-byte aligned declaration
   if (tid == 0) {
@@ -192,7 +214,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (a.status) atomicCAS(a.status, 0, code);
     }
   };
-  auto tile_lo = [&](int j, int& nk, bool& own) {
+  auto tile_lo = [&](int jl, int& nk, bool& own) {
+    const int j = jl + j0;
     own = j >= n_ctx;
     if (!own) {
       const int lo = ctx_lo + j * BN;
@@ -288,33 +311,42 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ptx::tmem_ld32(tmem_lane + (uint32_t)st * BN + 32, hi32);
       ptx::tmem_wait_ld();
     }
-    // visibility of the 64 key columns for this row
-    unsigned long long vis = nk >= 64 ? ~0ull : ((1ull << nk) - 1ull);
-    if (own) {
-      const int lim = tok - (j - n_ctx) * BN + 1;  // columns [0, lim) are at or before this row's token
-      vis = lim <= 0 ? 0ull : (lim >= 64 ? vis : (vis & ((1ull << lim) - 1ull)));
-    } else if (ctx_check) {
-      const unsigned v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
-      const unsigned v1 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + 32 + lane));
-      vis &= ((unsigned long long)v1 << 32) | v0;
-    }
+    // Tiles that lie fully inside the visible region need no per-element masking (the common case);
+    // ragged tails, the causal diagonal and padded context ranges take the masked path.
+    const int own_off = (j + j0 - n_ctx) * BN;
+    const bool need_mask = nk < BN || (own && own_off + BN - 1 > t0) || (!own && ctx_check);
     float mx = -INFINITY;
+    if (!need_mask) {
 #pragma unroll
-    for (int c = 0; c < 64; ++c) {
-      const float s = ((vis >> c) & 1ull) ? __uint_as_float(sr[c]) * a.scale_log2 : -INFINITY;
-      sr[c] = __float_as_uint(s);
-      mx = fmaxf(mx, s);
+      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+    } else {
+      int lim = nk;  // columns [0, lim) are visible to this row
+      if (own) lim = max(0, min(nk, tok - own_off + 1));
+      unsigned v0 = 0xffffffffu, v1 = 0xffffffffu;
+      if (!own && ctx_check) {
+        v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
+        v1 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + 32 + lane));
+      }
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
+        const float sv = ok ? __uint_as_float(sr[c]) : -INFINITY;
+        sr[c] = __float_as_uint(sv);
+        mx = fmaxf(mx, sv);
+      }
     }
+    mx *= a.scale_log2;  // scale > 0, so the max commutes with it
     float m_new = fmaxf(m_run, mx);
     if (m_run != -INFINITY && m_new - m_run <= kLazy) m_new = m_run;  // keep the old reference: p <= 2^8
     const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-    const float corr = exp2f(m_run - m_ref);  // 1 when unchanged, 0 on the first visible tile
+    const float corr = ptx::ex2(m_run - m_ref);  // 1 when unchanged, 0 on the first visible tile
+    const float neg_ref = -m_ref;
     float psum = 0.f;
     uint32_t pk[32];
 #pragma unroll
     for (int c = 0; c < 64; c += 2) {
-      const float p0 = exp2f(__uint_as_float(sr[c]) - m_ref);
-      const float p1 = exp2f(__uint_as_float(sr[c + 1]) - m_ref);
+      const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_ref));
+      const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_ref));
       psum += p0 + p1;
       __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
       pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -359,10 +391,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   }
 
-  // ---- epilogue: O / l -> bf16 -> staging (reusing the Q tile) -> coalesced stores ---------------
+  // ---- epilogue ---------------------------------------------------------------------------------
   wait(kBarO, (uint32_t)(n_tiles - 1) & 1u, 7);
   ptx::tc_fence_after_sync();
-  {
+  if (split) {
+    // un-normalised partial (O, max, sum) of this key chunk; merged by attn_combine_kernel
+    const int64_t prow = (((int64_t)b * a.N + n) * a.lq_max + tok) * a.n_split + chunk;
+#pragma unroll 1
+    for (int ch = 0; ch < HD / 32; ++ch) {
+      uint32_t orow[32];
+      ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+      ptx::tmem_wait_ld();
+      if (active && tok < a.lq_max) {
+        float4* dst = reinterpret_cast<float4*>(a.part_o + prow * HD + ch * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          dst[i] = make_float4(__uint_as_float(orow[4 * i]), __uint_as_float(orow[4 * i + 1]),
+                               __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
+      }
+    }
+    if (active && tok < a.lq_max) a.part_ml[prow] = make_float2(m_run, l_run);
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+  } else {
+    // O / l -> bf16 -> staging (reusing the Q tile) -> coalesced stores
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll 1
     for (int ch = 0; ch < HD / 32; ++ch) {
@@ -385,33 +437,87 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     if (active && a.lse != nullptr)
       a.lse[((int64_t)b * a.N + n) * a.S + start + tok] = (m_run + log2f(l_run)) * 0.6931471805599453f;
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  for (int it = 0; it < 16; ++it) {
-    const int rr = warp * 32 + it * 2 + (lane >> 4);
-    const int piece = lane & 15;
-    const int rtok = t0 + (rr >> a.g_shift);
-    if (rtok < len) {
-      const uint8_t* src = smem + kOffQ + (uint32_t)(piece >> 3) * (BM * 128) + (uint32_t)rr * 128 +
-                           (((piece & 7) ^ (rr & 7)) << 4);
-      __nv_bfloat16* dst = ob + (int64_t)(start + rtok) * a.o.ss + (int64_t)(g * G + (rr & (G - 1))) * a.o.sh + piece * 8;
-      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    for (int it = 0; it < 16; ++it) {
+      const int rr = warp * 32 + it * 2 + (lane >> 4);
+      const int piece = lane & 15;
+      const int rtok = t0 + (rr >> a.g_shift);
+      if (rtok < len) {
+        const uint8_t* src = smem + kOffQ + (uint32_t)(piece >> 3) * (BM * 128) + (uint32_t)rr * 128 +
+                             (((piece & 7) ^ (rr & 7)) << 4);
+        __nv_bfloat16* dst = ob + (int64_t)(start + rtok) * a.o.ss + (int64_t)(g * G + (rr & (G - 1))) * a.o.sh + piece * 8;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+      }
     }
   }
   if (warp == 0) ptx::tmem_dealloc(tmem, kTmemCols);
 }
 
+
+// Merge the key-chunk partials of the query block: one warp per (prompt, head, query token).
+__global__ void __launch_bounds__(128) attn_combine_kernel(TcArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int64_t total = (int64_t)a.B * a.N * a.lq_max;
+  if (w >= total) return;
+  const int tok = (int)(w % a.lq_max);
+  const int n = (int)((w / a.lq_max) % a.N);
+  const int b = (int)(w / ((int64_t)a.lq_max * a.N));
+  const int start = a.blk_start[(size_t)b * a.M + a.M - 1], len = a.blk_len[(size_t)b * a.M + a.M - 1];
+  if (tok >= len) return;
+  const float2* ml = a.part_ml + w * a.n_split;
+  float mx = -INFINITY;
+  for (int c = 0; c < a.n_split; ++c) mx = fmaxf(mx, ml[c].x);
+  const float ref = (mx == -INFINITY) ? 0.f : mx;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+  for (int c = 0; c < a.n_split; ++c) {
+    const float2 x = ml[c];
+    if (x.y > 0.f) {  // chunks that saw no key carry no output
+      const float wgt = exp2f(x.x - ref);
+      const float4 o = *reinterpret_cast<const float4*>(a.part_o + (w * a.n_split + c) * HD + lane * 4);
+      acc.x = fmaf(o.x, wgt, acc.x); acc.y = fmaf(o.y, wgt, acc.y);
+      acc.z = fmaf(o.z, wgt, acc.z); acc.w = fmaf(o.w, wgt, acc.w);
+      l = fmaf(x.y, wgt, l);
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.sb + (int64_t)(start + tok) * a.o.ss +
+                       (int64_t)n * a.o.sh + lane * 4;
+  store4(dst, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+  if (a.lse != nullptr && lane == 0) a.lse[((int64_t)b * a.N + n) * a.S + start + tok] = (ref + log2f(l)) * 0.6931471805599453f;
+}
+
 }  // namespace
 
-size_t attn_tc_workspace(const brk_attn_params&) { return 0; }
+// Key chunks for the query block.  Its context is every earlier token of the prompt (S is the only
+// bound known on the host), walked 64 keys per step by a single CTA per 128 rows; cutting it into
+// chunks of about 1024 keys keeps that serial chain short and gives the SMs enough CTAs.
+static int tc_splits(const brk_attn_params& p) {
+  if (p.M < 2) return 1;
+  int n = (p.S + 1023) / 1024;
+  return n < 1 ? 1 : (n > 32 ? 32 : n);
+}
 
-int attn_tc_launch(const brk_attn_params& p, void*, size_t, cudaStream_t st) {
+size_t attn_tc_workspace(const brk_attn_params& p) {
+  const int ns = tc_splits(p);
+  if (ns <= 1) return 0;
+  const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
+  return rows * HD * sizeof(float) + rows * sizeof(float2);
+}
+
+int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
   BRK_REQUIRE(p.dtype == BRK_BF16 && p.D == HD, BRK_E_UNSUPPORTED,
               "tcgen05 attention needs bf16 and head_dim 128 (dtype %d, head_dim %d)", p.dtype, p.D);
   const int G = p.N / p.Nk;
   BRK_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, BRK_E_UNSUPPORTED, "tcgen05 attention needs N/Nk in {1,2,4,8}, got %d", G);
-  BRK_REQUIRE(p.B * p.Nk <= 65535 && p.M <= 65535, BRK_E_UNSUPPORTED, "grid too large: B*Nk=%d M=%d", p.B * p.Nk, p.M);
+  const int ns = tc_splits(p);
+  BRK_REQUIRE(p.B * p.Nk <= 65535 && p.M + ns <= 65535, BRK_E_UNSUPPORTED, "grid too large: B*Nk=%d M=%d", p.B * p.Nk, p.M);
+  BRK_REQUIRE(p.scale > 0.f, BRK_E_ARG, "softmax scale must be positive");
+  const size_t need = attn_tc_workspace(p);
+  BRK_REQUIRE(need == 0 || (ws != nullptr && ws_bytes >= need && ((uintptr_t)ws & 15) == 0), BRK_E_WORKSPACE,
+              "attention workspace: %zu bytes (16-byte aligned) needed, %zu given", need, ws_bytes);
   int gs = 0;
   while ((1 << gs) < G) ++gs;
   const int TOK = BM / G;
@@ -425,6 +531,7 @@ int attn_tc_launch(const brk_attn_params& p, void*, size_t, cudaStream_t st) {
   BRK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     BRK_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    BRK_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   TcArgs a;
@@ -436,9 +543,19 @@ int attn_tc_launch(const brk_attn_params& p, void*, size_t, cudaStream_t st) {
   a.B = p.B; a.N = p.N; a.Nk = p.Nk; a.S = p.S; a.M = p.M;
   a.G = G; a.g_shift = gs;
   a.scale_log2 = p.scale * 1.4426950408889634f;
-  dim3 grid((p.max_block_len + TOK - 1) / TOK, p.M, p.B * p.Nk);
+  a.n_split = ns;
+  a.lq_max = p.max_block_len;
+  const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
+  a.part_o = ns > 1 ? reinterpret_cast<float*>(ws) : nullptr;
+  a.part_ml = ns > 1 ? reinterpret_cast<float2*>(reinterpret_cast<float*>(ws) + rows * HD) : nullptr;
+  dim3 grid((p.max_block_len + TOK - 1) / TOK, (p.M - 1) + ns, p.B * p.Nk);
   attn_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, a);
   BRK_CUDA(cudaGetLastError());
+  if (ns > 1) {
+    const int64_t warps = (int64_t)p.B * p.N * p.max_block_len;
+    attn_combine_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(a);
+    BRK_CUDA(cudaGetLastError());
+  }
   return BRK_OK;
 }
 

@@ -6,10 +6,10 @@
 //                        the G query heads of the group) and keeps an online
 //                        (max, sum-exp) per signal row; the CTA writes one
 //                        (max, sum) pair per (head, row, document).
-//   doc_finalize_kernel  one CTA per prompt: merges the per-document pairs
-//                        into the softmax over all document tokens, emits the
-//                        per-document probability mass and the mean/temperature
-//                        logits.
+//   doc_finalize_kernel  one warp per (prompt, head, row): merges the
+//                        per-document pairs into the softmax over all document
+//                        tokens and emits the per-document probability mass.
+//   doc_logits_kernel    mean over heads and rows / temperature.
 //   raw_scores_kernel    compatibility output: raw masked logits of the last R
 //                        slots against every slot.
 #include "brk_common.cuh"
@@ -59,18 +59,26 @@ __device__ __forceinline__ void key_dots(const T* __restrict__ kp, const float* 
   }
 }
 
+// One CTA per (document, prompt, KV head).  Each warp stages 32 key rows at a time in shared memory
+// with fully coalesced 16-byte loads (all in flight together), then every lane owns one key: its
+// dot products against the G*R staged query rows read the key from shared memory (row stride padded
+// by 16 bytes, conflict-free for 16-byte accesses) and the query rows as broadcasts.
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
+  constexpr int kRowBytes = D * (int)sizeof(T);
+  constexpr int kPitch = kRowBytes + 16;
+  constexpr int kChunks = kRowBytes / 16;  // 16-byte pieces per key row
   extern __shared__ __align__(16) float smem[];
   const int G = a.N / a.Nk;
   const int GR = G * a.R;
   float* qs = smem;                                    // [GR][D], scaled by scale*log2(e)
   float2* red = reinterpret_cast<float2*>(qs + GR * D);  // [kThreads/32][kRowBatch]
+  unsigned char* ktile = reinterpret_cast<unsigned char*>(red + (kThreads / 32) * kRowBatch);  // [warps][32][kPitch]
 
   const int nd = a.M - 2;
   const int d = blockIdx.x;
   const int b = blockIdx.y / a.Nk, g = blockIdx.y % a.Nk;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int start = a.blk_start[(size_t)b * a.M + 1 + d];
   const int len = a.blk_len[(size_t)b * a.M + 1 + d];
 
@@ -86,18 +94,33 @@ __global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
   }
   __syncthreads();
 
-  const T* kb = reinterpret_cast<const T*>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)g * a.k.sh;
+  const unsigned char* kb = reinterpret_cast<const unsigned char*>(
+      reinterpret_cast<const T*>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)g * a.k.sh);
+  const int64_t row_stride = a.k.ss * (int64_t)sizeof(T);
+  unsigned char* my_tile = ktile + (size_t)warp * 32 * kPitch;
   for (int r0 = 0; r0 < GR; r0 += kRowBatch) {
     const int nrows = min(kRowBatch, GR - r0);
     float m[kRowBatch], l[kRowBatch];
 #pragma unroll
     for (int i = 0; i < kRowBatch; ++i) { m[i] = -INFINITY; l[i] = 0.f; }
-    for (int t = tid; t < len; t += kThreads) {
-      float acc[kRowBatch];
-      key_dots<T, D>(kb + (int64_t)(start + t) * a.k.ss, qs + r0 * D, nrows, acc);
+    for (int base = warp * 32; base < len; base += kThreads) {
+      const int nkeys = min(32, len - base);
+      __syncwarp();
 #pragma unroll
-      for (int i = 0; i < kRowBatch; ++i)
-        if (i < nrows) merge_ml(m[i], l[i], acc[i], 1.f);
+      for (int i = 0; i < kChunks; ++i) {
+        const int idx = lane + 32 * i, row = idx / kChunks, ch = idx % kChunks;
+        if (row < nkeys)
+          *reinterpret_cast<uint4*>(my_tile + row * kPitch + ch * 16) =
+              *reinterpret_cast<const uint4*>(kb + (int64_t)(start + base + row) * row_stride + ch * 16);
+      }
+      __syncwarp();
+      if (lane < nkeys) {
+        float acc[kRowBatch];
+        key_dots<T, D>(reinterpret_cast<const T*>(my_tile + lane * kPitch), qs + r0 * D, nrows, acc);
+#pragma unroll
+        for (int i = 0; i < kRowBatch; ++i)
+          if (i < nrows) merge_ml(m[i], l[i], acc[i], 1.f);
+      }
     }
     // warp then CTA reduction, fixed order
 #pragma unroll
@@ -110,9 +133,9 @@ __global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
       }
     }
     __syncthreads();
-    if ((tid & 31) == 0) {
+    if (lane == 0) {
 #pragma unroll
-      for (int i = 0; i < kRowBatch; ++i) red[(tid >> 5) * kRowBatch + i] = make_float2(m[i], l[i]);
+      for (int i = 0; i < kRowBatch; ++i) red[warp * kRowBatch + i] = make_float2(m[i], l[i]);
     }
     __syncthreads();
     if (tid < nrows) {
@@ -128,46 +151,34 @@ __global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
   }
 }
 
-__device__ __forceinline__ float block_reduce(float v, bool is_max, float* scratch) {
-  const int tid = threadIdx.x;
+// One warp per (prompt, head, signal row): softmax over all documents from the per-document pairs.
+__global__ void __launch_bounds__(128) doc_finalize_kernel(const float2* __restrict__ partial, float* __restrict__ mass,
+                                                           int total_rows, int nd) {
+  const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (w >= total_rows) return;
+  const float2* p = partial + (size_t)w * nd;
+  float mx = -INFINITY;
+  for (int d = lane; d < nd; d += 32) mx = fmaxf(mx, p[d].x);
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    const float o = __shfl_xor_sync(0xffffffffu, v, off);
-    v = is_max ? fmaxf(v, o) : v + o;
-  }
-  __syncthreads();
-  if ((tid & 31) == 0) scratch[tid >> 5] = v;
-  __syncthreads();
-  float r = is_max ? -INFINITY : 0.f;
-  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
-  return r;
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  const float ref = (mx == -INFINITY) ? 0.f : mx;
+  float z = 0.f;
+  for (int d = lane; d < nd; d += 32) z += p[d].y * exp2f(p[d].x - ref);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
+  const float inv = z > 0.f ? 1.f / z : 0.f;
+  for (int d = lane; d < nd; d += 32) mass[(size_t)w * nd + d] = p[d].y * exp2f(p[d].x - ref) * inv;
 }
 
-__global__ void __launch_bounds__(256) doc_finalize_kernel(const float2* __restrict__ partial, float* __restrict__ mass,
-                                                           float* __restrict__ logits, int NR, int nd,
-                                                           float inv_count_temp) {
-  extern __shared__ float acc[];  // [nd]
-  __shared__ float scratch[8];
-  const int b = blockIdx.x, tid = threadIdx.x;
-  for (int d = tid; d < nd; d += blockDim.x) acc[d] = 0.f;
-  for (int nr = 0; nr < NR; ++nr) {
-    const float2* p = partial + ((size_t)b * NR + nr) * nd;
-    float mx = -INFINITY;
-    for (int d = tid; d < nd; d += blockDim.x) mx = fmaxf(mx, p[d].x);
-    mx = block_reduce(mx, true, scratch);
-    const float ref = (mx == -INFINITY) ? 0.f : mx;
-    float z = 0.f;
-    for (int d = tid; d < nd; d += blockDim.x) z += p[d].y * exp2f(p[d].x - ref);
-    z = block_reduce(z, false, scratch);
-    const float inv = z > 0.f ? 1.f / z : 0.f;
-    for (int d = tid; d < nd; d += blockDim.x) {
-      const float w = p[d].y * exp2f(p[d].x - ref) * inv;
-      mass[((size_t)b * NR + nr) * nd + d] = w;
-      acc[d] += w;  // each d is owned by one thread: deterministic
-    }
-  }
-  if (logits != nullptr)
-    for (int d = tid; d < nd; d += blockDim.x) logits[(size_t)b * nd + d] = acc[d] * inv_count_temp;
+// logits[b, d] = mean over (head, row) of mass / temperature; one thread per document, fixed order.
+__global__ void __launch_bounds__(128) doc_logits_kernel(const float* __restrict__ mass, float* __restrict__ logits,
+                                                         int NR, int nd, float inv_count_temp) {
+  const int b = blockIdx.y, d = blockIdx.x * 128 + threadIdx.x;
+  if (d >= nd) return;
+  const float* p = mass + (size_t)b * NR * nd + d;
+  float acc = 0.f;
+  for (int i = 0; i < NR; ++i) acc += p[(size_t)i * nd];
+  logits[(size_t)b * nd + d] = acc * inv_count_temp;
 }
 
 // block index of a slot, or -1 for padding (blk_start is non-decreasing)
@@ -272,7 +283,8 @@ int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cuda
   a.partial = reinterpret_cast<float2*>(ws);
   const int nd = p.M - 2, G = p.N / p.Nk;
   dim3 grid(nd, p.B * p.Nk);
-  const size_t sm = (size_t)G * p.R * p.D * 4 + (kThreads / 32) * kRowBatch * sizeof(float2);
+  const size_t pitch = (size_t)p.D * (p.dtype == BRK_BF16 ? 2 : 4) + 16;
+  const size_t sm = (size_t)G * p.R * p.D * 4 + (kThreads / 32) * kRowBatch * sizeof(float2) + (kThreads / 32) * 32 * pitch;
   auto launch = [&](auto kern) -> int {
     if (sm > 48 * 1024) BRK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
     kern<<<grid, kThreads, sm, st>>>(a);
@@ -282,9 +294,14 @@ int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cuda
   if (p.dtype == BRK_BF16) rc = p.D == 128 ? launch(doc_partial_kernel<__nv_bfloat16, 128>) : launch(doc_partial_kernel<__nv_bfloat16, 64>);
   else rc = p.D == 128 ? launch(doc_partial_kernel<float, 128>) : launch(doc_partial_kernel<float, 64>);
   if (rc) return rc;
-  doc_finalize_kernel<<<p.B, 256, (size_t)nd * 4, st>>>(a.partial, p.doc_mass, p.logits, p.N * p.R, nd,
-                                                        1.f / ((float)(p.N * p.R) * p.temperature));
+  const int total_rows = p.B * p.N * p.R;
+  doc_finalize_kernel<<<(total_rows + 3) / 4, 128, 0, st>>>(a.partial, p.doc_mass, total_rows, nd);
   BRK_CUDA(cudaGetLastError());
+  if (p.logits != nullptr) {
+    doc_logits_kernel<<<dim3((nd + 127) / 128, p.B), 128, 0, st>>>(p.doc_mass, p.logits, p.N * p.R, nd,
+                                                                    1.f / ((float)(p.N * p.R) * p.temperature));
+    BRK_CUDA(cudaGetLastError());
+  }
   return BRK_OK;
 }
 

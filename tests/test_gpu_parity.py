@@ -92,6 +92,7 @@ def test_attention_simt_vs_oracle(case, dt):
 TC_CASES = [  # B, N, Nk, M, H, seed  (head_dim 128)
     (1, 4, 1, 3, 64, 11), (2, 8, 2, 5, 80, 12), (1, 8, 2, 4, 160, 13), (1, 4, 4, 4, 96, 14), (1, 8, 4, 3, 48, 15),
     (1, 8, 1, 3, 32, 16), (2, 4, 1, 1, 128, 17), (2, 4, 1, 2, 72, 18), (1, 32, 8, 12, 160, 19),
+    (2, 8, 2, 40, 64, 20), (1, 4, 1, 3, 1024, 21),
 ]
 
 
