@@ -18,7 +18,7 @@ ERRORS = {-1: "BRK_E_ARG", -2: "BRK_E_UNSUPPORTED", -3: "BRK_E_WORKSPACE", -4: "
 
 EXPORTS = ("brk_version", "brk_last_error", "brk_device_check", "brk_spans_from_mask",
            "brk_attn_fwd_workspace_bytes", "brk_attn_fwd", "brk_doc_scores_workspace_bytes",
-           "brk_doc_scores", "brk_raw_scores", "brk_rmsnorm", "brk_rope", "brk_silu_mul")
+           "brk_doc_scores", "brk_doc_scores_static", "brk_raw_scores", "brk_rmsnorm", "brk_rope", "brk_silu_mul")
 
 
 class View(C.Structure):
@@ -70,6 +70,8 @@ def lib() -> C.CDLL:
     L.brk_doc_scores_workspace_bytes.argtypes = [C.POINTER(ScoreParams)]
     L.brk_doc_scores.restype = C.c_int
     L.brk_doc_scores.argtypes = [C.POINTER(ScoreParams), C.c_void_p, C.c_size_t, C.c_void_p]
+    L.brk_doc_scores_static.restype = C.c_int
+    L.brk_doc_scores_static.argtypes = [C.POINTER(ScoreParams), C.c_void_p]
     L.brk_raw_scores.restype = C.c_int
     L.brk_raw_scores.argtypes = [C.POINTER(ScoreParams), C.c_void_p, C.c_void_p]
     L.brk_rmsnorm.restype = C.c_int

@@ -104,6 +104,11 @@ int brk_doc_scores(const brk_score_params* p, void* workspace, size_t workspace_
   return doc_scores_launch(*p, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+int brk_doc_scores_static(const brk_score_params* p, void* stream) {
+  BRK_REQUIRE(p != nullptr, BRK_E_ARG, "params is null");
+  return doc_scores_static_launch(*p, (cudaStream_t)stream);
+}
+
 int brk_raw_scores(const brk_score_params* p, void* out, void* stream) {
   BRK_REQUIRE(p != nullptr, BRK_E_ARG, "params is null");
   return raw_scores_launch(*p, out, (cudaStream_t)stream);

@@ -81,6 +81,7 @@ namespace brk {
 size_t doc_scores_workspace(const brk_score_params& p);
 int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
 int raw_scores_launch(const brk_score_params& p, void* out, cudaStream_t st);
+int doc_scores_static_launch(const brk_score_params& p, cudaStream_t st);
 int spans_launch(const uint8_t* mask, int B, int M, int H, int32_t* start, int32_t* len, cudaStream_t st);
 int rmsnorm_launch(int dtype, const void* x, void* residual, const void* w, void* out, int64_t rows, int hidden,
                    float eps, cudaStream_t st);

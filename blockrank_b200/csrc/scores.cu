@@ -305,6 +305,36 @@ int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cuda
   return BRK_OK;
 }
 
+// ---- allocation-free variant ----------------------------------------------------------------
+// Scratch for brk_doc_scores_static: the (max, sum) pairs that doc_partial_kernel writes and
+// doc_finalize_kernel reads live in this fixed array instead of a caller-provided workspace.
+// It is part of the library image, so every device that loads the library holds these bytes
+// until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[BRK_STATIC_SCRATCH_BYTES];
+
+int doc_scores_static_launch(const brk_score_params& p, cudaStream_t st) {
+  const size_t need = doc_scores_workspace(p);
+  BRK_REQUIRE(need <= (size_t)BRK_STATIC_SCRATCH_BYTES, BRK_E_WORKSPACE,
+              "brk_doc_scores_static: B*N*R*(M-2)*8 = %zu bytes of scratch needed, the built-in array holds %zu; "
+              "use brk_doc_scores with a caller workspace for this size",
+              need, (size_t)BRK_STATIC_SCRATCH_BYTES);
+  // In host code the array's name is only a handle; the kernels need its device address, which
+  // differs per device.  It is looked up once per device, with that device current.
+  static void* dev_ptr[64] = {};
+  int dev = 0;
+  BRK_CUDA(cudaGetDevice(&dev));
+  BRK_REQUIRE(dev >= 0 && dev < 64, BRK_E_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (dev_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    BRK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    BRK_REQUIRE(ptr != nullptr, BRK_E_CUDA, "cudaGetSymbolAddress returned a null scratch address");
+    dev_ptr[dev] = ptr;
+  }
+  // every (prompt, head, row, document) pair is overwritten by doc_partial_kernel before
+  // doc_finalize_kernel reads it, so nothing left by an earlier call has to be cleared
+  return doc_scores_launch(p, dev_ptr[dev], (size_t)BRK_STATIC_SCRATCH_BYTES, st);
+}
+
 int raw_scores_launch(const brk_score_params& p, void* out, cudaStream_t st) {
   int rc = check(p);
   if (rc) return rc;

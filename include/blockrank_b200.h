@@ -131,6 +131,30 @@ typedef struct brk_score_params {
 BRK_API size_t brk_doc_scores_workspace_bytes(const brk_score_params* p);
 BRK_API int brk_doc_scores(const brk_score_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Allocation-free variant of brk_doc_scores.  It has no counterpart in the reference.
+ *
+ * Same inputs, outputs and results as brk_doc_scores, but the scratch between its two kernels
+ * is a fixed BRK_STATIC_SCRATCH_BYTES array inside the library, so neither the library nor the
+ * caller has to obtain device memory for it.  It is meant for callers that must not allocate
+ * at the point of the call: a serving loop that reserved all of its device memory at start-up
+ * and treats any later cudaMalloc as a bug (it synchronises the device and can fail under
+ * memory pressure), or an embedding of the library into a host (another language runtime, a
+ * plugin sandbox) that owns no device allocator at all and can only pass through the input and
+ * output buffers it was given.
+ *
+ * Limits and rules:
+ *  - B*N*R*(M-2)*8 bytes must fit in BRK_STATIC_SCRATCH_BYTES (4 MiB; e.g. 8 prompts x 32 heads
+ *    x 2 rows x 1024 documents); larger problems are refused with BRK_E_WORKSPACE and a message
+ *    that names both sizes.  Each GPU that loads the library holds the array until exit.
+ *  - The first call on a device looks up the array's device address; make that first call
+ *    outside any stream capture.
+ *  - All calls on a device share the one array.  Nothing needs clearing between calls (every
+ *    entry is rewritten before it is read), but two calls that can run at the same time on the
+ *    GPU -- different streams, or different host threads -- race on it: serialise them.
+ *  - No cudaMalloc / cudaFree / allocating library routine is called. */
+#define BRK_STATIC_SCRATCH_BYTES (4u << 20)
+BRK_API int brk_doc_scores_static(const brk_score_params* p, void* stream);
+
 /* Compatibility output of the reference's second return value: raw scaled,
  * masked logits of the last R slots of the prompt against every slot,
  * out[B, N, R, S] in `dtype`, masked entries = 0.7 * lowest finite value of the
