@@ -1,25 +1,31 @@
 // BlockRank attention forward on the sm_100a tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// Work item = one CTA = (prompt b, block m, KV head g, tile of 128/G query
-// tokens) x the G query heads that share KV head g: the 128 rows of the MMA
-// tile are (token, head) pairs, so one K/V tile in shared memory serves the
-// whole GQA group and the Q tile is a single 3-D TMA box of the [B,S,N,D]
-// tensor.  Only live key tiles are visited:
+// Persistent, warp-specialised kernel: one CTA per SM walks a static list of work items.
+// A work item is (prompt b, KV head g, block m, pair of row tiles[, key chunk]); a row tile is
+// 128 MMA rows = 128/G consecutive query tokens x the G query heads that share KV head g, so
+// one K/V tile in shared memory serves the whole GQA group and a Q tile is one 3-D TMA box of
+// the [B,S,N,D] tensor.  The two row tiles of a pair ("chains") share the item's K/V tiles and
+// are processed in ping-pong: while one chain's 128 softmax threads work on their S tile, the
+// tensor core runs the other chain's MMAs.
+//
+// Only live key tiles (64 keys) are visited:
 //   block 0            : own keys, causal
 //   document block     : the prefix block's keys, then own keys, causal
-//   query (last) block : every slot of the earlier blocks, then own keys, causal
-// Per key tile (64 keys): S = Q K^T (tcgen05.mma, both operands K-major in
-// 128B-swizzled shared memory, accumulator in TMEM) -> each of the 128 threads
-// owns one row: tcgen05.ld, mask, online softmax (base 2, lazy rescale), P as
-// bf16 into swizzled shared memory -> O += P V (V is the MN-major B operand,
-// accumulator stays in TMEM across tiles).  K and V tiles are double buffered
-// and prefetched by TMA; S is double buffered in TMEM so the next QK^T runs
-// under the current softmax.  Two CTAs fit per SM (112 KB smem, 256 TMEM
-// columns each), which overlaps one CTA's softmax with the other's MMAs.
+//   query (last) block : every slot of the earlier blocks, then own keys, causal; its context
+//                        is cut into key chunks, each a work item that leaves an un-normalised
+//                        partial (O, max, sum); attn_combine_kernel merges them.
 //
-// Every mbarrier wait is bounded; on expiry the CTA records a code in the
-// caller's status word, stops waiting, and still runs to its normal exit
-// (TMEM is released on every path).
+// Roles (320 threads):
+//   warps 0-3 / 4-7  softmax + epilogue of chain 0 / 1 (thread = row = TMEM lane)
+//   warp 8           TMA producer: Q tiles and a 4-stage K/V ring, running ahead across items
+//   warp 9           MMA issuer: S = Q K^T (both operands K-major, 128B swizzle) and O += P V
+//                    (P from swizzled shared memory, V as the MN-major B operand)
+// O stays in TMEM across the key tiles of an item; softmax is base-2, online, with a lazy
+// rescale (O is only touched when the running max grows by more than 2^8).
+//
+// Shared memory 225 KB: Q 2x32 KB, P 2x16 KB, K/V ring 4x32 KB.  TMEM: 2 x (S 64 + O 128)
+// columns.  No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the
+// thread records a code in the caller's status word, stops waiting and runs to the normal exit.
 #include <cuda.h>
 
 #include "brk_common.cuh"
@@ -58,25 +64,52 @@ int make_tmap_bf16(CUtensorMap* out, const void* ptr, int D, int heads, int S, i
   return BRK_OK;
 }
 
+#ifdef BRK_TC_TIMING
+// Development aid: per-phase cycle counters (accumulated by one thread per role over all CTAs).
+__device__ unsigned long long g_tc_cycles[32];
+#define TC_T0() const long long tc_t0_ = clock64()
+#define TC_ACC(slot, pred)                                                          \
+  do {                                                                              \
+    if (pred) atomicAdd(&g_tc_cycles[slot], (unsigned long long)(clock64() - tc_t_)); \
+    tc_t_ = clock64();                                                              \
+  } while (0)
+#else
+#define TC_ACC(slot, pred) do { } while (0)
+#endif
+
 namespace {
 
-constexpr int BM = 128;  // query rows (token, head) per CTA
+constexpr int BM = 128;  // query rows (token, head) per row tile
 constexpr int BN = 64;   // keys per tile
 constexpr int HD = 128;  // head dim
-constexpr int kThreads = 128;
-constexpr uint32_t kQBytes = 2 * BM * 128;   // two 64-wide halves of D
-constexpr uint32_t kKVBytes = 2 * BN * 128;  // one K or V tile
+constexpr int kStages = 4;
+constexpr int kThreads = 320;
+constexpr uint32_t kQBytes = 2 * BM * 128;  // two 64-wide halves of D
+constexpr uint32_t kKBytes = 2 * BN * 128;  // one K (or V) tile
+constexpr uint32_t kStageBytes = 2 * kKBytes;
 constexpr uint32_t kPBytes = BM * 128;
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + kQBytes;
-constexpr uint32_t kOffV = kOffK + 2 * kKVBytes;
-constexpr uint32_t kOffP = kOffV + 2 * kKVBytes;
-constexpr uint32_t kOffBar = kOffP + kPBytes;
-constexpr uint32_t kSmemBytes = kOffBar + 256 + 512;  // barriers + slack for the 1024-byte round-up
-constexpr uint32_t kTmemCols = 256;                   // S0 [0,64) S1 [64,128) O [128,256)
-constexpr uint32_t kColO = 128;
-constexpr float kLazy = 8.f;  // rescale O only when the running max grows by more than 2^8
+constexpr uint32_t kOffP = kOffQ + 2 * kQBytes;
+constexpr uint32_t kOffKV = kOffP + 2 * kPBytes;
+constexpr uint32_t kOffBar = kOffKV + kStages * kStageBytes;
+constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;  // barriers + slack for the 1024-byte round-up
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kChainCols = 192;  // per chain: S [0,64) then O [64,192)
+constexpr uint32_t kColO = 64;
+constexpr float kLazy = 8.f;
 constexpr uint32_t kWaitBudget = 1u << 18;
+
+enum {
+  kQFull = 0,    // +chain  TMA -> MMA: Q tile landed
+  kQFree = 2,    // +chain  MMA -> TMA: every QK^T of the item has read Q
+  kSFull = 4,    // +chain  MMA -> softmax: S tile complete
+  kPFull = 6,    // +chain  softmax -> MMA: P in shared memory, S consumed (128 arrivals)
+  kPVDone = 8,   // +chain  MMA -> softmax: P V of a tile complete
+  kOFree = 10,   // +chain  softmax -> MMA: O read out of TMEM (128 arrivals)
+  kKVFull = 12,  // +stage  TMA -> MMA
+  kKVFree = 16,  // +stage  MMA -> TMA
+  kNumBars = 20
+};
 
 struct TcArgs {
   View o;
@@ -85,15 +118,105 @@ struct TcArgs {
   const int32_t* blk_len;
   int32_t* status;
   int B, N, Nk, S, M;
-  int G, g_shift;  // query heads per KV head, log2
+  int G, g_shift;   // query heads per KV head, log2
   float scale_log2;
-  int n_split;     // key chunks the query block's context is cut into (1 = no split)
-  int lq_max;      // rows per (prompt, head) in the partial buffers (= max_block_len)
-  float* part_o;   // [B, N, lq_max, n_split, 128] un-normalised partial outputs
-  float2* part_ml; // [B, N, lq_max, n_split] (running max in log2 units, sum)
+  int n_split;      // key chunks of the query block's context (1 = no split)
+  int lq_max;       // rows per (prompt, head) in the partial buffers (= max_block_len)
+  int pairs;        // row-tile pairs per block (covers max_block_len)
+  int total_items;
+  float* part_o;    // [B, N, lq_max, n_split, 128] un-normalised partial outputs
+  float2* part_ml;  // [B, N, lq_max, n_split] (running max in log2 units, sum)
 };
 
-enum { kBarQ = 0, kBarK0 = 1, kBarK1 = 2, kBarV0 = 3, kBarV1 = 4, kBarS0 = 5, kBarS1 = 6, kBarO = 7, kNumBars = 8 };
+struct Item {
+  int b, g, m, chunk;
+  int start, len;        // span of block m
+  int t0[2];             // first token of each chain's row tile
+  int n_x[2];            // key tiles visible to each chain (a prefix of the item's tile list)
+  int ctx_lo, ctx_hi;    // context key range (slots)
+  int n_ctx, j0;         // context tiles of the block, first tile of this item
+  int n_tiles, own_n;
+  bool split, valid;
+};
+
+// Work list order: query-block chunks first (longest), then blocks M-2 .. 0.
+__device__ __forceinline__ Item decode_item(const TcArgs& a, int idx) {
+  Item it;
+  const int nbg = a.B * a.Nk;
+  const int TOK = BM >> a.g_shift;
+  const int sec1 = nbg * a.n_split * a.pairs;
+  int p, bg;
+  if (idx < sec1) {
+    p = idx / (nbg * a.n_split);
+    const int r = idx % (nbg * a.n_split);
+    it.chunk = r / nbg;
+    bg = r % nbg;
+    it.m = a.M - 1;
+  } else {
+    const int i2 = idx - sec1;
+    p = i2 / (nbg * (a.M - 1));
+    const int r = i2 % (nbg * (a.M - 1));
+    it.m = a.M - 2 - r / nbg;
+    bg = r % nbg;
+    it.chunk = 0;
+  }
+  it.b = bg / a.Nk;
+  it.g = bg % a.Nk;
+  const int32_t* bs = a.blk_start + (size_t)it.b * a.M;
+  const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
+  it.start = bs[it.m];
+  it.len = bl[it.m];
+  it.t0[0] = 2 * p * TOK;
+  it.t0[1] = it.t0[0] + TOK;
+  it.valid = it.t0[0] < it.len;
+  it.split = it.m == a.M - 1 && a.n_split > 1;
+  it.ctx_lo = it.ctx_hi = 0;
+  it.n_ctx = it.j0 = it.n_tiles = it.own_n = 0;
+  it.n_x[0] = it.n_x[1] = 0;
+  if (!it.valid) return it;
+  if (it.m > 0) {
+    it.ctx_lo = bs[0];
+    it.ctx_hi = (it.m < a.M - 1) ? bs[0] + bl[0] : bs[a.M - 2] + bl[a.M - 2];
+  }
+  const bool on1 = it.t0[1] < it.len;
+  it.own_n = min(it.len, (on1 ? it.t0[1] : it.t0[0]) + TOK);
+  it.n_ctx = (it.ctx_hi - it.ctx_lo + BN - 1) / BN;
+  const int own_tiles = (it.own_n + BN - 1) / BN;
+  int j1 = it.n_ctx + own_tiles;
+  if (it.split) {
+    const int per = (it.n_ctx + a.n_split - 1) / a.n_split;
+    it.j0 = min(it.n_ctx, it.chunk * per);
+    if (it.chunk != a.n_split - 1) j1 = min(it.n_ctx, it.j0 + per);
+  }
+  it.n_tiles = j1 - it.j0;
+  if (it.n_tiles <= 0) {  // a chunk without tiles: nothing to do (its partial stays neutral)
+    it.valid = false;
+    it.n_tiles = 0;
+    return it;
+  }
+  // own tiles visible to chain x: those starting at or before its last token
+  for (int x = 0; x < 2; ++x) {
+    if (x == 1 && !on1) break;
+    const int own_x = min(own_tiles, (min(it.len, it.t0[x] + TOK) + BN - 1) / BN);
+    it.n_x[x] = max(0, min(j1, it.n_ctx + own_x) - it.j0);
+  }
+  return it;
+}
+
+// tile j of the item -> first key slot, number of keys, whether it lies in the item's own block
+__device__ __forceinline__ int tile_lo(const Item& it, int j, int& nk, bool& own, int& own_off) {
+  const int jg = j + it.j0;
+  own = jg >= it.n_ctx;
+  if (!own) {
+    const int lo = it.ctx_lo + jg * BN;
+    nk = min(BN, it.ctx_hi - lo);
+    own_off = 0;
+    return lo;
+  }
+  own_off = (jg - it.n_ctx) * BN;
+  nk = min(BN, it.own_n - own_off);
+  return it.start + own_off;
+}
 
 // slot -> is it inside some block?  (blk_start is non-decreasing)
 __device__ __forceinline__ bool slot_valid(const int32_t* bs, const int32_t* bl, int M, int s) {
@@ -106,91 +229,46 @@ __device__ __forceinline__ bool slot_valid(const int32_t* bs, const int32_t* bl,
   return m >= 0 && s < bs[m] + bl[m];
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.z / a.Nk, g = blockIdx.z % a.Nk;
-  // grid.y: first the n_split key chunks of the query block (longest work first), then blocks M-2 .. 0
-  const bool is_last = (int)blockIdx.y < a.n_split;
-  const int chunk = is_last ? (int)blockIdx.y : 0;
-  const int m = is_last ? a.M - 1 : a.M - 2 - ((int)blockIdx.y - a.n_split);
-  const int tile = blockIdx.x;
-  const int G = a.G, TOK = BM >> a.g_shift;
-  const int32_t* bs = a.blk_start + (size_t)b * a.M;
-  const int32_t* bl = a.blk_len + (size_t)b * a.M;
-  const int start = bs[m], len = bl[m];
+  const int G = a.G;
+#ifdef BRK_TC_TIMING
+  const long long tc_kernel_t0 = clock64();
+#endif
 
-  __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.sb;
-  if (tile == 0 && chunk == 0) {
-    // padding slots in front of this block (and behind the last one) are written as zeros
-    const int gap0 = (m == 0) ? 0 : bs[m - 1] + bl[m - 1];
-    const int per_row = G * (HD / 8);
-    for (int pass = 0; pass < 2; ++pass) {
-      const int lo = pass == 0 ? gap0 : start + len;
-      const int hi = pass == 0 ? start : ((m == a.M - 1) ? a.S : start + len);
-      for (int i = tid; i < (hi - lo) * per_row; i += kThreads) {
-        const int s = lo + i / per_row, rem = i % per_row;
-        const int h = g * G + rem / (HD / 8), d8 = rem % (HD / 8);
-        *reinterpret_cast<uint4*>(ob + (int64_t)s * a.o.ss + (int64_t)h * a.o.sh + d8 * 8) = make_uint4(0, 0, 0, 0);
-      }
+  // ---- padding slots of the output are written as zeros (gaps in front of / behind blocks) ----
+  for (int gi = blockIdx.x; gi < a.B * (a.M + 1); gi += gridDim.x) {
+    const int b = gi / (a.M + 1), m = gi % (a.M + 1);
+    const int32_t* bs = a.blk_start + (size_t)b * a.M;
+    const int32_t* bl = a.blk_len + (size_t)b * a.M;
+    const int lo = (m == 0) ? 0 : bs[m - 1] + bl[m - 1];
+    const int hi = (m == a.M) ? a.S : bs[m];
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.sb;
+    const int per_row = a.N * (HD / 8);
+    for (int i = tid; i < (hi - lo) * per_row; i += kThreads) {
+      const int s = lo + i / per_row, rem = i % per_row;
+      *reinterpret_cast<uint4*>(ob + (int64_t)s * a.o.ss + (int64_t)(rem / (HD / 8)) * a.o.sh + (rem % (HD / 8)) * 8) =
+          make_uint4(0, 0, 0, 0);
     }
   }
-  const int t0 = tile * TOK;
-  if (t0 >= len) return;  // uniform for the CTA, nothing allocated yet
 
-  // ---- shared memory carve-up ----------------------------------------------------------------
+  // ---- shared memory carve-up, barriers, TMEM ---------------------------------------------------
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (sbase - raw);
-  const uint32_t sQ = sbase + kOffQ, sK = sbase + kOffK, sV = sbase + kOffV, sP = sbase + kOffP;
   const uint32_t sBar = sbase + kOffBar;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + kNumBars * 8);
-  int* red_i = reinterpret_cast<int*>(smem + kOffBar + 128);
   auto bar = [&](int i) { return sBar + (uint32_t)i * 8u; };
 
-  // ---- key ranges ------------------------------------------------------------------------
-  int ctx_lo = 0, ctx_hi = 0;
-  bool ctx_check = false;  // context range may contain padding slots
-  if (m > 0 && a.M > 1) {
-    ctx_lo = bs[0];
-    if (m < a.M - 1) {
-      ctx_hi = bs[0] + bl[0];
-    } else {
-      ctx_hi = bs[a.M - 2] + bl[a.M - 2];
-      int part = 0;
-      for (int i = tid; i < a.M - 1; i += kThreads) part += bl[i];
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-      if (lane == 0) red_i[warp] = part;
-      __syncthreads();
-      ctx_check = (red_i[0] + red_i[1] + red_i[2] + red_i[3]) != (ctx_hi - ctx_lo);
-    }
-  }
-  const int own_n = min(len, t0 + TOK);
-  const int n_ctx = (ctx_hi - ctx_lo + BN - 1) / BN;
-  // this CTA's share of the tile list: everything, or one chunk of the context (+ own keys for the last chunk)
-  int j0 = 0, n_tiles = n_ctx + (own_n + BN - 1) / BN;
-  const bool split = is_last && a.n_split > 1;
-  if (split) {
-    const int per = (n_ctx + a.n_split - 1) / a.n_split;
-    j0 = min(n_ctx, chunk * per);
-    const int j1 = (chunk == a.n_split - 1) ? n_tiles : min(n_ctx, j0 + per);
-    n_tiles = j1 - j0;
-    if (n_tiles <= 0) {  // empty chunk: leave a neutral partial for the combine step
-      const int rr = tid, rtok = t0 + (rr >> a.g_shift);
-      if (rtok < len && rtok < a.lq_max)
-        a.part_ml[(((int64_t)b * a.N + g * G + (rr & (G - 1))) * a.lq_max + rtok) * a.n_split + chunk] =
-            make_float2(-INFINITY, 0.f);
-      return;
-    }
-  }
-
-  bool failed = (sbase - raw) > 512u;  // cannot happen with the 1024-byte aligned declaration
+  bool failed = false;
   if (tid == 0) {
-    for (int i = 0; i < kNumBars; ++i) ptx::mbar_init(bar(i), 1);
+    for (int i = 0; i < kNumBars; ++i) {
+      const bool many = (i >= kPFull && i < kPFull + 2) || (i >= kOFree && i < kOFree + 2);
+      ptx::mbar_init(bar(i), many ? 128u : 1u);
+    }
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmQ);
     ptx::prefetch_tmap(&tmK);
@@ -205,255 +283,365 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_lane = tmem + ((uint32_t)(warp * 32) << 16);
 
   auto wait = [&](int i, uint32_t parity, int code) {
     if (failed) return;
-    if (!ptx::mbar_wait(bar(i), parity, kWaitBudget)) {
+    if (!ptx::mbar_wait(bar(i), parity & 1u, kWaitBudget)) {
       failed = true;
       if (a.status) atomicCAS(a.status, 0, code);
     }
   };
-  auto tile_lo = [&](int jl, int& nk, bool& own) {
-    const int j = jl + j0;
-    own = j >= n_ctx;
-    if (!own) {
-      const int lo = ctx_lo + j * BN;
-      nk = min(BN, ctx_hi - lo);
-      return lo;
-    }
-    const int off = (j - n_ctx) * BN;
-    nk = min(BN, own_n - off);
-    return start + off;
-  };
-  auto load_kv = [&](const CUtensorMap* tm, uint32_t dst, int barrier, int j) {
-    int nk; bool own;
-    const int lo = tile_lo(j, nk, own);
-    ptx::mbar_expect_tx(bar(barrier), kKVBytes);
-    ptx::tma_load_4d(dst, tm, bar(barrier), 0, g, lo, b);
-    ptx::tma_load_4d(dst + BN * 128, tm, bar(barrier), 64, g, lo, b);
-  };
-  auto issue_qk = [&](int j) {
-    int nk; bool own;
-    tile_lo(j, nk, own);
-    const int st = j & 1;
-    const uint32_t idesc = ptx::idesc_bf16(BM, (uint32_t)((nk + 15) & ~15), 0, 0);
-    const uint32_t kb = sK + (uint32_t)st * kKVBytes;
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-      const uint64_t ad = ptx::smem_desc_sw128(sQ + (uint32_t)(ks >> 2) * (BM * 128) + (uint32_t)(ks & 3) * 32, 16, 1024);
-      const uint64_t bd = ptx::smem_desc_sw128(kb + (uint32_t)(ks >> 2) * (BN * 128) + (uint32_t)(ks & 3) * 32, 16, 1024);
-      ptx::mma_ss(tmem + (uint32_t)st * BN, ad, bd, idesc, ks > 0);
-    }
-    ptx::mma_commit(bar(kBarS0 + st));
-  };
-  auto issue_pv = [&](int j) {
-    int nk; bool own;
-    tile_lo(j, nk, own);
-    const int st = j & 1;
-    const uint32_t idesc = ptx::idesc_bf16(BM, HD, 0, 1);
-    const uint32_t vb = sV + (uint32_t)st * kKVBytes;
-    const int ksteps = (nk + 15) >> 4;
-    for (int ks = 0; ks < ksteps; ++ks) {
-      const uint64_t ad = ptx::smem_desc_sw128(sP + (uint32_t)ks * 32, 16, 1024);
-      const uint64_t bd = ptx::smem_desc_sw128(vb + (uint32_t)ks * (16 * 128), BN * 128, 1024);
-      ptx::mma_ss(tmem + kColO, ad, bd, idesc, (j > 0 || ks > 0) ? 1u : 0u);
-    }
-    ptx::mma_commit(bar(kBarO));
-  };
 
-  // ---- prologue: Q, the first two K/V tiles, first QK^T ----------------------------------------
-  if (tid == 0) {
-    ptx::mbar_expect_tx(bar(kBarQ), kQBytes);
-    ptx::tma_load_4d(sQ, &tmQ, bar(kBarQ), 0, g * G, start + t0, b);
-    ptx::tma_load_4d(sQ + BM * 128, &tmQ, bar(kBarQ), 64, g * G, start + t0, b);
-    load_kv(&tmK, sK, kBarK0, 0);
-    load_kv(&tmV, sV, kBarV0, 0);
-    if (n_tiles > 1) {
-      load_kv(&tmK, sK + kKVBytes, kBarK1, 1);
-      load_kv(&tmV, sV + kKVBytes, kBarV1, 1);
-    }
-    wait(kBarQ, 0, 1);
-    wait(kBarK0, 0, 2);
-    ptx::tc_fence_after_sync();
-    issue_qk(0);
-  }
-  __syncwarp();
-
-  const int r = tid;                 // row of the tile = TMEM lane
-  const int tok = t0 + (r >> a.g_shift);
-  const int n = g * G + (r & (G - 1));
-  const bool active = tok < len;
-  float m_run = -INFINITY, l_run = 0.f;
-
-  for (int j = 0; j < n_tiles; ++j) {
-    const int st = j & 1;
-    const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-    int nk; bool own;
-    const int lo = tile_lo(j, nk, own);
-
-    if (tid == 0 && j + 1 < n_tiles) {
-      wait(kBarK0 + ((j + 1) & 1), (uint32_t)((j + 1) >> 1) & 1u, 3);
-      ptx::tc_fence_after_sync();
-      issue_qk(j + 1);  // runs under this tile's softmax
-    }
-    __syncwarp();
-    wait(kBarS0 + st, ph, 4);
-    ptx::tc_fence_after_sync();
-    if (tid == 0 && j + 2 < n_tiles) load_kv(&tmK, sK + (uint32_t)st * kKVBytes, kBarK0 + st, j + 2);  // K stage is free
-    __syncwarp();
-
-    uint32_t sr[64];
-    {
-      uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
-      uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
-      ptx::tmem_ld32(tmem_lane + (uint32_t)st * BN, lo32);
-      ptx::tmem_ld32(tmem_lane + (uint32_t)st * BN + 32, hi32);
-      ptx::tmem_wait_ld();
-    }
-    // Tiles that lie fully inside the visible region need no per-element masking (the common case);
-    // ragged tails, the causal diagonal and padded context ranges take the masked path.
-    const int own_off = (j + j0 - n_ctx) * BN;
-    const bool need_mask = nk < BN || (own && own_off + BN - 1 > t0) || (!own && ctx_check);
-    float mx = -INFINITY;
-    if (!need_mask) {
-#pragma unroll
-      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
-    } else {
-      int lim = nk;  // columns [0, lim) are visible to this row
-      if (own) lim = max(0, min(nk, tok - own_off + 1));
-      unsigned v0 = 0xffffffffu, v1 = 0xffffffffu;
-      if (!own && ctx_check) {
-        v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
-        v1 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + 32 + lane));
-      }
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
-        const float sv = ok ? __uint_as_float(sr[c]) : -INFINITY;
-        sr[c] = __float_as_uint(sv);
-        mx = fmaxf(mx, sv);
+  if (warp == 8) {
+    // =============================== TMA producer ===============================================
+    if (lane == 0) {
+      uint32_t kv_cnt = 0, q_loads[2] = {0, 0};
+      for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+        const Item it = decode_item(a, idx);
+        if (!it.valid) continue;
+        for (int x = 0; x < 2; ++x) {
+          if (it.n_x[x] == 0) continue;
+#ifdef BRK_TC_TIMING
+          long long tc_t_ = clock64();
+#endif
+          if (q_loads[x] > 0) wait(kQFree + x, q_loads[x] - 1, 10 + x);
+          TC_ACC(24, true);  // producer: wait Q free
+          const uint32_t dst = sbase + kOffQ + (uint32_t)x * kQBytes;
+          ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
+          ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, it.g * G, it.start + it.t0[x], it.b);
+          ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, it.g * G, it.start + it.t0[x], it.b);
+          ++q_loads[x];
+        }
+        for (int j = 0; j < it.n_tiles; ++j) {
+          int nk, own_off; bool own;
+          const int lo = tile_lo(it, j, nk, own, own_off);
+          const uint32_t st = kv_cnt % kStages, use = kv_cnt / kStages;
+#ifdef BRK_TC_TIMING
+          long long tc_t_ = clock64();
+#endif
+          if (use > 0) wait(kKVFree + st, use - 1, 12);
+          TC_ACC(25, true);  // producer: wait KV stage free
+          const uint32_t dst = sbase + kOffKV + st * kStageBytes;
+          ptx::mbar_expect_tx(bar(kKVFull + st), kStageBytes);
+          ptx::tma_load_4d(dst, &tmK, bar(kKVFull + st), 0, it.g, lo, it.b);
+          ptx::tma_load_4d(dst + BN * 128, &tmK, bar(kKVFull + st), 64, it.g, lo, it.b);
+          ptx::tma_load_4d(dst + kKBytes, &tmV, bar(kKVFull + st), 0, it.g, lo, it.b);
+          ptx::tma_load_4d(dst + kKBytes + BN * 128, &tmV, bar(kKVFull + st), 64, it.g, lo, it.b);
+          ++kv_cnt;
+        }
       }
     }
-    mx *= a.scale_log2;  // scale > 0, so the max commutes with it
-    float m_new = fmaxf(m_run, mx);
-    if (m_run != -INFINITY && m_new - m_run <= kLazy) m_new = m_run;  // keep the old reference: p <= 2^8
-    const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-    const float corr = ptx::ex2(m_run - m_ref);  // 1 when unchanged, 0 on the first visible tile
-    const float neg_ref = -m_ref;
-    float psum = 0.f;
-    uint32_t pk[32];
+  } else if (warp == 9) {
+    // =============================== MMA issuer =================================================
+    if (lane == 0) {
+      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0};
+      // Descriptors are built once: every operand buffer has a fixed address, and stepping along K
+      // or to another ring stage only adds a constant to the 16-byte-unit start-address field.
+      const uint32_t idesc_pv = ptx::idesc_bf16(BM, HD, 0, 1);
+      const uint32_t idesc_qk0 = ptx::idesc_bf16(BM, 0, 0, 0);
+      const uint64_t q_desc0 = ptx::smem_desc_sw128(sbase + kOffQ, 16, 1024);
+      const uint64_t p_desc0 = ptx::smem_desc_sw128(sbase + kOffP, 16, 1024);
+      const uint64_t k_desc0 = ptx::smem_desc_sw128(sbase + kOffKV, 16, 1024);
+      const uint64_t v_desc0 = ptx::smem_desc_sw128(sbase + kOffKV + kKBytes, BN * 128, 1024);
+      auto issue_qk = [&](int x, int nk, bool last, uint32_t st) {
+        const uint32_t idesc = idesc_qk0 | ((uint32_t)((nk + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
+        const uint64_t ad = q_desc0 + (uint64_t)((uint32_t)x * (kQBytes >> 4));
+        const uint64_t bd = k_desc0 + (uint64_t)(st * (kStageBytes >> 4));
+        const uint32_t d = tmem + (uint32_t)x * kChainCols;
 #pragma unroll
-    for (int c = 0; c < 64; c += 2) {
-      const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_ref));
-      const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_ref));
-      psum += p0 + p1;
-      __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-      pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
+          const uint32_t boff = (uint32_t)(ks >> 2) * ((BN * 128) >> 4) + (uint32_t)(ks & 3) * 2;
+          ptx::mma_ss(d, ad + aoff, bd + boff, idesc, ks > 0);
+        }
+        ptx::mma_commit(bar(kSFull + x));
+        if (last) ptx::mma_commit(bar(kQFree + x));  // last read of this chain's Q tile
+      };
+      auto issue_pv = [&](int x, int nk, bool first, uint32_t st) {
+        const uint64_t ad = p_desc0 + (uint64_t)((uint32_t)x * (kPBytes >> 4));
+        const uint64_t bd = v_desc0 + (uint64_t)(st * (kStageBytes >> 4));
+        const uint32_t d = tmem + (uint32_t)x * kChainCols + kColO;
+        const int ksteps = (nk + 15) >> 4;
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks)
+          if (ks < ksteps) ptx::mma_ss(d, ad + (uint32_t)ks * 2, bd + (uint32_t)ks * ((16 * 128) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
+        ptx::mma_commit(bar(kPVDone + x));
+      };
+      for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+        const Item it = decode_item(a, idx);
+        if (!it.valid) continue;
+        const int n0 = it.n_x[0], n1 = it.n_x[1];
+#ifdef BRK_TC_TIMING
+        long long tc_t_ = clock64();
+#endif
+#pragma unroll
+        for (int x = 0; x < 2; ++x)
+          if ((x == 0 ? n0 : n1) > 0) { wait(kQFull + x, q_uses[x], 20 + x); ++q_uses[x]; }
+        TC_ACC(16, true);  // MMA: wait Q
+        int kv_waited = -1;
+        auto need_kv = [&](int j) {
+          if (kv_waited >= j) return;
+          const uint32_t gidx = kv_cnt + (uint32_t)j;
+          wait(kKVFull + gidx % kStages, gidx / kStages, 22);
+          kv_waited = j;
+        };
+        auto tile_nk = [&](int j) {
+          int nk, own_off; bool own;
+          tile_lo(it, j, nk, own, own_off);
+          return nk;
+        };
+        need_kv(0);
+        TC_ACC(17, true);  // MMA: wait first KV
+        ptx::tc_fence_after_sync();
+        {
+          const int nk = tile_nk(0);
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int nx = x == 0 ? n0 : n1;
+            if (nx > 0) issue_qk(x, nk, nx == 1, kv_cnt % kStages);
+          }
+        }
+        int nk_cur = tile_nk(0);
+        for (int j = 0; j < it.n_tiles; ++j) {
+          const uint32_t st = (kv_cnt + (uint32_t)j) % kStages;
+          const int nk_next = (j + 1 < it.n_tiles) ? tile_nk(j + 1) : 0;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int nx = x == 0 ? n0 : n1;
+            if (j >= nx) continue;
+            TC_ACC(18, true);  // MMA: issue work
+            wait(kPFull + x, p_seen[x], 24 + x);
+            ++p_seen[x];
+            TC_ACC(19, true);  // MMA: wait P
+            if (j == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
+            TC_ACC(20, true);  // MMA: wait O free
+            ptx::tc_fence_after_sync();
+            issue_pv(x, nk_cur, j == 0, st);
+            if (j + 1 < nx) {
+              TC_ACC(18, true);
+              need_kv(j + 1);
+              TC_ACC(21, true);  // MMA: wait next KV
+              ptx::tc_fence_after_sync();
+              issue_qk(x, nk_next, j + 2 == nx, (kv_cnt + (uint32_t)j + 1) % kStages);
+            }
+          }
+          ptx::mma_commit(bar(kKVFree + st));  // both chains' MMAs on this stage are queued
+          nk_cur = nk_next;
+        }
+        kv_cnt += (uint32_t)it.n_tiles;
+#pragma unroll
+        for (int x = 0; x < 2; ++x)
+          if ((x == 0 ? n0 : n1) > 0) ++items_done[x];
+      }
     }
-    l_run = l_run * corr + psum;
-    const bool changed = m_new != m_run;
-    m_run = m_new;
+  } else {
+    // =============================== softmax + epilogue, chain x ================================
+    const int x = warp >> 2;
+    const int r = tid & 127;  // row of the tile = TMEM lane
+    const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)x * kChainCols;
+    uint8_t* pbuf = smem + kOffP + (uint32_t)x * kPBytes;
+    uint32_t s_seen = 0, pv_seen = 0;
+    for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+      const Item it = decode_item(a, idx);
+      if (!it.valid || it.n_x[x] == 0) continue;
+      const int32_t* bs = a.blk_start + (size_t)it.b * a.M;
+      const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
+      const int tok = it.t0[x] + (r >> a.g_shift);
+      const int n = it.g * G + (r & (G - 1));
+      const bool active = tok < it.len;
+      bool ctx_check = false;  // the query block's context may contain padding slots
+      if (it.m == a.M - 1 && it.m > 0) {
+        int part = 0;
+        for (int i = lane; i < a.M - 1; i += 32) part += bl[i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+        ctx_check = part != (it.ctx_hi - it.ctx_lo);
+      }
+      float m_run = -INFINITY, l_run = 0.f;
+#ifdef BRK_TC_TIMING
+      long long tc_t_ = clock64();
+      const bool tc_me = (tid == 0);
+#endif
+      for (int j = 0; j < it.n_x[x]; ++j) {
+        int nk, own_off; bool own;
+        const int lo = tile_lo(it, j, nk, own, own_off);
+        TC_ACC(0, tc_me);  // decode / loop overhead
+        wait(kSFull + x, s_seen, 30 + x);
+        ++s_seen;
+        TC_ACC(1, tc_me);  // wait S
+        ptx::tc_fence_after_sync();
+        __syncwarp();
+        uint32_t sr[64];
+        {
+          uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
+          uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
+          ptx::tmem_ld32(tmem_lane, lo32);
+          ptx::tmem_ld32(tmem_lane + 32, hi32);
+          ptx::tmem_wait_ld();
+        }
+        TC_ACC(2, tc_me);  // TMEM load of S
+        // Tiles fully inside the visible region need no per-element masking (the common case);
+        // ragged tails, the causal diagonal and padded context ranges take the masked path.
+        const bool need_mask = nk < BN || (own && own_off + BN - 1 > it.t0[x]) || (!own && ctx_check);
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+        if (!need_mask) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+        } else {
+          int lim = nk;  // columns [0, lim) are visible to this row
+          if (own) lim = max(0, min(nk, tok - own_off + 1));
+          unsigned v0 = 0xffffffffu, v1 = 0xffffffffu;
+          if (!own && ctx_check) {
+            v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
+            v1 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + 32 + lane));
+          }
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
+            const float sv = ok ? __uint_as_float(sr[c]) : -INFINITY;
+            sr[c] = __float_as_uint(sv);
+            mx4[c & 3] = fmaxf(mx4[c & 3], sv);
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
+        float m_new = fmaxf(m_run, mx);
+        if (m_run != -INFINITY && m_new - m_run <= kLazy) m_new = m_run;  // keep the old reference: p <= 2^8
+        const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = ptx::ex2(m_run - m_ref);  // 1 when unchanged, 0 on the first visible tile
+        const float neg_ref = -m_ref;
+        float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_ref));
+          const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_ref));
+          ps4[(c >> 1) & 3] += p0 + p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        l_run = l_run * corr + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+        const bool changed = m_new != m_run;
+        m_run = m_new;
+        TC_ACC(3, tc_me);  // softmax math
 
-    if (j > 0) {
-      wait(kBarO, (uint32_t)(j - 1) & 1u, 5);  // PV of the previous tile done: O stable, P and a V stage free
+        if (j > 0) {
+          wait(kPVDone + x, pv_seen, 32 + x);  // previous P V done: O stable, P buffer free
+          ++pv_seen;
+          TC_ACC(4, tc_me);  // wait previous PV
+          ptx::tc_fence_after_sync();
+          if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll 1
+            for (int ch = 0; ch < HD / 32; ++ch) {
+              uint32_t orow[32];
+              ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
+              ptx::tmem_st32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+            }
+            ptx::tmem_wait_st();
+          }
+          TC_ACC(5, tc_me);  // O rescale
+        }
+        // P row -> shared memory in the K-major 128B-swizzled layout the MMA reads
+        {
+          uint8_t* prow = pbuf + (uint32_t)r * 128;
+#pragma unroll
+          for (int c16 = 0; c16 < 8; ++c16)
+            *reinterpret_cast<uint4*>(prow + ((c16 ^ (r & 7)) << 4)) =
+                make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(bar(kPFull + x));
+        TC_ACC(6, tc_me);  // P store + arrive
+      }
+
+      // ---- epilogue ----
+      wait(kPVDone + x, pv_seen, 34 + x);
+      ++pv_seen;
+      TC_ACC(7, tc_me);  // wait last PV
       ptx::tc_fence_after_sync();
-      if (tid == 0 && j + 1 < n_tiles) load_kv(&tmV, sV + (uint32_t)((j + 1) & 1) * kKVBytes, kBarV0 + ((j + 1) & 1), j + 1);
       __syncwarp();
-      if (__any_sync(0xffffffffu, changed)) {
+      if (it.split) {
+        // un-normalised partial (O, max, sum) of this key chunk; merged by attn_combine_kernel
+        const bool wr = active && tok < a.lq_max;
+        const int64_t prow = (((int64_t)it.b * a.N + n) * a.lq_max + tok) * a.n_split + it.chunk;
 #pragma unroll 1
         for (int ch = 0; ch < HD / 32; ++ch) {
           uint32_t orow[32];
           ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
           ptx::tmem_wait_ld();
+          if (wr) {
+            float4* dst = reinterpret_cast<float4*>(a.part_o + prow * HD + ch * 32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
-          ptx::tmem_st32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(orow[4 * i]), __uint_as_float(orow[4 * i + 1]),
+                                   __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
+          }
         }
-        ptx::tmem_wait_st();
-      }
-    }
-    // P row -> shared memory in the K-major 128B-swizzled layout the MMA reads
-    {
-      uint8_t* prow = smem + kOffP + (uint32_t)r * 128;
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(bar(kOFree + x));
+        if (wr) a.part_ml[prow] = make_float2(m_run, l_run);
+      } else {
+        // O / l -> bf16 -> staging in this chain's P buffer, one 64-wide half of D at a time ->
+        // coalesced 16-byte stores
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb;
+        const int wt = tid & 127;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll 1
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t orow[32];
+            ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)(2 * h + cc) * 32, orow);
+            ptx::tmem_wait_ld();
+            uint8_t* srow = pbuf + (uint32_t)r * 128;
 #pragma unroll
-      for (int c16 = 0; c16 < 8; ++c16)
-        *reinterpret_cast<uint4*>(prow + ((c16 ^ (r & 7)) << 4)) =
-            make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
-    }
-    ptx::fence_proxy_async_smem();
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      ptx::tc_fence_after_sync();
-      wait(kBarV0 + st, ph, 6);
-      issue_pv(j);
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(orow[q4 * 8 + 2 * i]) * inv,
+                                                          __uint_as_float(orow[q4 * 8 + 2 * i + 1]) * inv);
+                w[i] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              const int c16 = cc * 4 + q4;
+              *reinterpret_cast<uint4*>(srow + ((c16 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+          if (h == 1) {  // O is out of TMEM: the next item's first P V may overwrite it
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(bar(kOFree + x));
+          }
+          ptx::named_bar_sync(1 + x, 128);
+          for (int itr = 0; itr < 8; ++itr) {
+            const int rr = itr * 16 + (wt >> 3), piece = wt & 7;
+            const int rtok = it.t0[x] + (rr >> a.g_shift);
+            if (rtok < it.len) {
+              const uint8_t* src = pbuf + (uint32_t)rr * 128 + ((piece ^ (rr & 7)) << 4);
+              __nv_bfloat16* dst = ob + (int64_t)(it.start + rtok) * a.o.ss +
+                                   (int64_t)(it.g * G + (rr & (G - 1))) * a.o.sh + h * 64 + piece * 8;
+              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+            }
+          }
+          ptx::named_bar_sync(1 + x, 128);
+        }
+        if (active && a.lse != nullptr)
+          a.lse[((int64_t)it.b * a.N + n) * a.S + it.start + tok] = (m_run + log2f(l_run)) * 0.6931471805599453f;
+      }
+      TC_ACC(8, tc_me);  // epilogue
     }
   }
 
-  // ---- epilogue ---------------------------------------------------------------------------------
-  wait(kBarO, (uint32_t)(n_tiles - 1) & 1u, 7);
-  ptx::tc_fence_after_sync();
-  if (split) {
-    // un-normalised partial (O, max, sum) of this key chunk; merged by attn_combine_kernel
-    const int64_t prow = (((int64_t)b * a.N + n) * a.lq_max + tok) * a.n_split + chunk;
-#pragma unroll 1
-    for (int ch = 0; ch < HD / 32; ++ch) {
-      uint32_t orow[32];
-      ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-      ptx::tmem_wait_ld();
-      if (active && tok < a.lq_max) {
-        float4* dst = reinterpret_cast<float4*>(a.part_o + prow * HD + ch * 32);
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          dst[i] = make_float4(__uint_as_float(orow[4 * i]), __uint_as_float(orow[4 * i + 1]),
-                               __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
-      }
-    }
-    if (active && tok < a.lq_max) a.part_ml[prow] = make_float2(m_run, l_run);
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-  } else {
-    // O / l -> bf16 -> staging (reusing the Q tile) -> coalesced stores
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-#pragma unroll 1
-    for (int ch = 0; ch < HD / 32; ++ch) {
-      uint32_t orow[32];
-      ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-      ptx::tmem_wait_ld();
-      uint8_t* srow = smem + kOffQ + (uint32_t)(ch >> 1) * (BM * 128) + (uint32_t)r * 128;
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(orow[q4 * 8 + 2 * i]) * inv,
-                                                   __uint_as_float(orow[q4 * 8 + 2 * i + 1]) * inv);
-          w[i] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        const int c16 = (ch & 1) * 4 + q4;
-        *reinterpret_cast<uint4*>(srow + ((c16 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-    if (active && a.lse != nullptr)
-      a.lse[((int64_t)b * a.N + n) * a.S + start + tok] = (m_run + log2f(l_run)) * 0.6931471805599453f;
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    for (int it = 0; it < 16; ++it) {
-      const int rr = warp * 32 + it * 2 + (lane >> 4);
-      const int piece = lane & 15;
-      const int rtok = t0 + (rr >> a.g_shift);
-      if (rtok < len) {
-        const uint8_t* src = smem + kOffQ + (uint32_t)(piece >> 3) * (BM * 128) + (uint32_t)rr * 128 +
-                             (((piece & 7) ^ (rr & 7)) << 4);
-        __nv_bfloat16* dst = ob + (int64_t)(start + rtok) * a.o.ss + (int64_t)(g * G + (rr & (G - 1))) * a.o.sh + piece * 8;
-        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-      }
-    }
-  }
+#ifdef BRK_TC_TIMING
+  if (tid == 0) atomicAdd(&g_tc_cycles[31], (unsigned long long)(clock64() - tc_kernel_t0));
+#endif
+  // ---- teardown ---------------------------------------------------------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
   if (warp == 0) ptx::tmem_dealloc(tmem, kTmemCols);
 }
-
 
 // Merge the key-chunk partials of the query block: one warp per (prompt, head, query token).
 __global__ void __launch_bounds__(128) attn_combine_kernel(TcArgs a) {
@@ -489,11 +677,17 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(TcArgs a) {
   if (a.lse != nullptr && lane == 0) a.lse[((int64_t)b * a.N + n) * a.S + start + tok] = (ref + log2f(l)) * 0.6931471805599453f;
 }
 
+// neutral partials for chunks that own no tile (the combine step skips sum == 0)
+__global__ void attn_clear_partials_kernel(float2* ml, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) ml[i] = make_float2(-INFINITY, 0.f);
+}
+
 }  // namespace
 
 // Key chunks for the query block.  Its context is every earlier token of the prompt (S is the only
-// bound known on the host), walked 64 keys per step by a single CTA per 128 rows; cutting it into
-// chunks of about 1024 keys keeps that serial chain short and gives the SMs enough CTAs.
+// bound known on the host), walked 64 keys per step per row tile; cutting it into chunks of about
+// 1024 keys keeps that serial chain short and spreads it over the SMs.
 static int tc_splits(const brk_attn_params& p) {
   if (p.M < 2) return 1;
   int n = (p.S + 1023) / 1024;
@@ -512,27 +706,32 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
               "tcgen05 attention needs bf16 and head_dim 128 (dtype %d, head_dim %d)", p.dtype, p.D);
   const int G = p.N / p.Nk;
   BRK_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, BRK_E_UNSUPPORTED, "tcgen05 attention needs N/Nk in {1,2,4,8}, got %d", G);
-  const int ns = tc_splits(p);
-  BRK_REQUIRE(p.B * p.Nk <= 65535 && p.M + ns <= 65535, BRK_E_UNSUPPORTED, "grid too large: B*Nk=%d M=%d", p.B * p.Nk, p.M);
   BRK_REQUIRE(p.scale > 0.f, BRK_E_ARG, "softmax scale must be positive");
+  const int ns = tc_splits(p);
   const size_t need = attn_tc_workspace(p);
   BRK_REQUIRE(need == 0 || (ws != nullptr && ws_bytes >= need && ((uintptr_t)ws & 15) == 0), BRK_E_WORKSPACE,
               "attention workspace: %zu bytes (16-byte aligned) needed, %zu given", need, ws_bytes);
   int gs = 0;
   while ((1 << gs) < G) ++gs;
   const int TOK = BM / G;
+  const int pairs = (p.max_block_len + 2 * TOK - 1) / (2 * TOK);
+  const int64_t total_items = (int64_t)p.B * p.Nk * pairs * (ns + p.M - 1);
+  BRK_REQUIRE(total_items < (1ll << 30), BRK_E_UNSUPPORTED, "too many work items (%lld)", (long long)total_items);
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_tmap_bf16(&tq, p.q.ptr, HD, p.N, p.S, p.B, p.q.stride_h, p.q.stride_s, p.q.stride_b, G, TOK))) return rc;
   if ((rc = make_tmap_bf16(&tk, p.k.ptr, HD, p.Nk, p.S, p.B, p.k.stride_h, p.k.stride_s, p.k.stride_b, 1, BN))) return rc;
   if ((rc = make_tmap_bf16(&tv, p.v.ptr, HD, p.Nk, p.S, p.B, p.v.stride_h, p.v.stride_s, p.v.stride_b, 1, BN))) return rc;
   static bool configured[64] = {};
+  static int sms[64] = {};
   int dev = 0;
   BRK_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
+  BRK_REQUIRE(dev >= 0 && dev < 64, BRK_E_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (!configured[dev]) {
     BRK_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    BRK_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+    sms[dev] = sm_count();
+    BRK_REQUIRE(sms[dev] > 0, BRK_E_CUDA, "could not read the SM count");
+    configured[dev] = true;
   }
   TcArgs a;
   a.o = make_view(p.o);
@@ -545,10 +744,16 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   a.scale_log2 = p.scale * 1.4426950408889634f;
   a.n_split = ns;
   a.lq_max = p.max_block_len;
+  a.pairs = pairs;
+  a.total_items = (int)total_items;
   const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
   a.part_o = ns > 1 ? reinterpret_cast<float*>(ws) : nullptr;
   a.part_ml = ns > 1 ? reinterpret_cast<float2*>(reinterpret_cast<float*>(ws) + rows * HD) : nullptr;
-  dim3 grid((p.max_block_len + TOK - 1) / TOK, (p.M - 1) + ns, p.B * p.Nk);
+  if (ns > 1) {
+    attn_clear_partials_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a.part_ml, (int64_t)rows);
+    BRK_CUDA(cudaGetLastError());
+  }
+  const int grid = (int)(total_items < sms[dev] ? total_items : sms[dev]);
   attn_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, a);
   BRK_CUDA(cudaGetLastError());
   if (ns > 1) {
@@ -558,5 +763,16 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   }
   return BRK_OK;
 }
+
+#ifdef BRK_TC_TIMING
+extern "C" __attribute__((visibility("default"))) int brk_debug_tc_cycles(unsigned long long* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, g_tc_cycles, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
+  if (reset) {
+    unsigned long long z[32] = {};
+    if (cudaMemcpyToSymbol(g_tc_cycles, z, sizeof(z)) != cudaSuccess) return -1;
+  }
+  return 0;
+}
+#endif
 
 }  // namespace brk

@@ -127,8 +127,9 @@ int brk_rope(int32_t dtype, void* q, int64_t q_row_stride, int32_t N, void* k, i
              int32_t D, const int32_t* pos, const float* inv_freq, int64_t T, void* stream) {
   BRK_REQUIRE((q || N == 0) && (k || Nk == 0) && pos && inv_freq, BRK_E_ARG, "null pointer");
   BRK_REQUIRE(dtype == BRK_BF16 || dtype == BRK_F32, BRK_E_UNSUPPORTED, "dtype %d", dtype);
-  BRK_REQUIRE(T > 0 && N >= 0 && Nk >= 0 && N + Nk > 0 && D > 0 && D % 2 == 0, BRK_E_ARG, "bad rope shape");
-  BRK_REQUIRE(T * (N + Nk) * (D / 2) / 256 < (1ll << 31), BRK_E_ARG, "rope problem too large");
+  BRK_REQUIRE(T > 0 && N >= 0 && Nk >= 0 && N + Nk > 0 && D > 0 && D % 16 == 0, BRK_E_ARG, "bad rope shape (head_dim must be a multiple of 16)");
+  BRK_REQUIRE((q == nullptr || (((uintptr_t)q & 15) == 0 && q_row_stride % 8 == 0)) && (k == nullptr || (((uintptr_t)k & 15) == 0 && k_row_stride % 8 == 0)), BRK_E_ARG, "rope rows must be 16-byte aligned");
+  BRK_REQUIRE(T * (D / 16) / 256 < (1ll << 31), BRK_E_ARG, "rope problem too large");
   return rope_launch(dtype, q, q_row_stride, N, k, k_row_stride, Nk, D, pos, inv_freq, T, (cudaStream_t)stream);
 }
 
@@ -137,7 +138,8 @@ int brk_silu_mul(int32_t dtype, const void* gate_up, void* out, int64_t rows, in
   BRK_REQUIRE(dtype == BRK_BF16 || dtype == BRK_F32, BRK_E_UNSUPPORTED, "dtype %d", dtype);
   BRK_REQUIRE(rows > 0 && inter > 0 && inter % 8 == 0, BRK_E_ARG, "bad silu_mul shape rows=%lld inter=%d",
               (long long)rows, inter);
-  BRK_REQUIRE(rows * (inter / 4) / 256 < (1ll << 31), BRK_E_ARG, "silu_mul problem too large");
+  BRK_REQUIRE(rows * (inter / 8) / 256 < (1ll << 31), BRK_E_ARG, "silu_mul problem too large");
+  BRK_REQUIRE((((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0, BRK_E_ARG, "silu_mul buffers must be 16-byte aligned");
   return silu_mul_launch(dtype, gate_up, out, rows, inter, (cudaStream_t)stream);
 }
 

@@ -66,43 +66,56 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, T
 }
 
 // ---- RoPE ---------------------------------------------------------------------
+// One thread per (row, 8 rotation pairs): the 8 angles are evaluated once and applied to every
+// query and key head of that row, with 16-byte loads and stores of both halves of each head.
 template <typename T>
-__global__ void rope_kernel(T* __restrict__ q, int64_t q_rs, int N, T* __restrict__ k, int64_t k_rs, int Nk, int D,
-                            const int32_t* __restrict__ pos, const float* __restrict__ inv_freq, int64_t T_rows) {
-  // one thread per (row, head, pair index i < D/2); heads of q then heads of k
-  const int half = D >> 1;
-  const int64_t per_row = (int64_t)(N + Nk) * half;
+__global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ q, int64_t q_rs, int N, T* __restrict__ k,
+                                                   int64_t k_rs, int Nk, int D, const int32_t* __restrict__ pos,
+                                                   const float* __restrict__ inv_freq, int64_t T_rows) {
+  const int half = D >> 1, chunks = half >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= T_rows * per_row) return;
-  const int64_t t = idx / per_row;
-  const int rem = (int)(idx % per_row);
-  const int h = rem / half, i = rem % half;
-  T* base = h < N ? q + t * q_rs + (int64_t)h * D : k + t * k_rs + (int64_t)(h - N) * D;
-  const float ang = (float)pos[t] * inv_freq[i];
-  float sn, cs;
-  sincosf(ang, &sn, &cs);
-  cs = Elem<T>::round(cs);
-  sn = Elem<T>::round(sn);
-  const float x1 = Elem<T>::load(base + i), x2 = Elem<T>::load(base + i + half);
-  // x*cos + rotate_half(x)*sin with each product rounded in the model dtype
-  const float o1 = Elem<T>::round(x1 * cs) + Elem<T>::round(-x2 * sn);
-  const float o2 = Elem<T>::round(x2 * cs) + Elem<T>::round(x1 * sn);
-  Elem<T>::store(base + i, o1);
-  Elem<T>::store(base + i + half, o2);
+  if (idx >= T_rows * chunks) return;
+  const int64_t t = idx / chunks;
+  const int i0 = (int)(idx % chunks) * 8;
+  const float p = (float)pos[t];
+  float cs[8], sn[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    sincosf(p * inv_freq[i0 + i], &sn[i], &cs[i]);
+    cs[i] = Elem<T>::round(cs[i]);
+    sn[i] = Elem<T>::round(sn[i]);
+  }
+  for (int h = 0; h < N + Nk; ++h) {
+    T* base = (h < N ? q + t * q_rs + (int64_t)h * D : k + t * k_rs + (int64_t)(h - N) * D) + i0;
+    float x1[8], x2[8], o1[8], o2[8];
+    load8(base, x1);
+    load8(base + half, x2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // x*cos + rotate_half(x)*sin with each product rounded in the model dtype
+      o1[i] = Elem<T>::round(x1[i] * cs[i]) + Elem<T>::round(-x2[i] * sn[i]);
+      o2[i] = Elem<T>::round(x2[i] * cs[i]) + Elem<T>::round(x1[i] * sn[i]);
+    }
+    store8(base, o1);
+    store8(base + half, o2);
+  }
 }
 
 // ---- SiLU(gate) * up ------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int inter) {
-  const int64_t per_row = inter / 4;
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows,
+                                                       int inter) {
+  const int64_t per_row = inter / 8;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * per_row) return;
   const int64_t r = idx / per_row;
-  const int c = (int)(idx % per_row) * 4;
-  const float4 g = load4(gu + r * 2 * inter + c);
-  const float4 u = load4(gu + r * 2 * inter + inter + c);
-  auto f = [](float x, float y) { return Elem<T>::round(x / (1.f + expf(-x))) * y; };
-  store4(out + r * inter + c, make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w)));
+  const int c = (int)(idx % per_row) * 8;
+  float g[8], u[8], o[8];
+  load8(gu + r * 2 * inter + c, g);
+  load8(gu + r * 2 * inter + inter + c, u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = Elem<T>::round(g[i] / (1.f + expf(-g[i]))) * u[i];
+  store8(out + r * inter + c, o);
 }
 
 }  // namespace
@@ -135,7 +148,7 @@ int rmsnorm_launch(int dtype, const void* x, void* residual, const void* w, void
 
 int rope_launch(int dtype, void* q, int64_t q_rs, int N, void* k, int64_t k_rs, int Nk, int D, const int32_t* pos,
                 const float* inv_freq, int64_t T, cudaStream_t st) {
-  const int64_t total = T * (N + Nk) * (D / 2);
+  const int64_t total = T * (D / 16);
   const int threads = 256;
   const int64_t blocks = (total + threads - 1) / threads;
   if (dtype == BRK_BF16)
@@ -148,7 +161,7 @@ int rope_launch(int dtype, void* q, int64_t q_rs, int N, void* k, int64_t k_rs, 
 }
 
 int silu_mul_launch(int dtype, const void* gu, void* out, int64_t rows, int inter, cudaStream_t st) {
-  const int64_t total = rows * (inter / 4);
+  const int64_t total = rows * (inter / 8);
   const int threads = 256;
   const int64_t blocks = (total + threads - 1) / threads;
   if (dtype == BRK_BF16)

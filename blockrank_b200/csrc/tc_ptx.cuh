@@ -23,6 +23,13 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Barrier among a subset of the CTA's warps (id 1..15, nthreads a multiple of 32).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 // Bounded wait on a phase parity. Returns false if the budget ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t budget = (1u << 22)) {
   for (uint32_t it = 0; it < budget; ++it) {

@@ -249,3 +249,75 @@ def test_standalone_op_config_parity():
     err = (logits.cpu().double() - exact_logits).abs().max().item()
     print(f"config-2 scores: max abs err {err:.3e}, min adjacent gap in top-11 {gap:.3e}")
     assert torch.equal(top_k, top_r) or gap < 10 * err, (gap, err)
+
+
+def _ragged_prompt(n_docs, seed, lo=32, hi=256):
+    g = torch.Generator().manual_seed(seed)
+    return [64] + torch.randint(lo, hi + 1, (n_docs,), generator=g).tolist() + [48]
+
+
+def test_ragged_long_list_packed_vs_oracle():
+    """Reduced ragged long-list case (60 documents of 32..256 tokens, padding-free layout): the
+    tcgen05 kernel against the oracle run on the reference's padded grid built from the same tokens."""
+    N, Nk, D = 32, 8, 128
+    bl = _ragged_prompt(60, seed=5)
+    start, ln, S, mbl = H_.packed_spans([bl])
+    g = torch.Generator().manual_seed(55)
+    qp = (torch.randn(1, S, N, D, generator=g) * 0.5).bfloat16()
+    kp = (torch.randn(1, S, Nk, D, generator=g) * 0.5).bfloat16()
+    vp = (torch.randn(1, S, Nk, D, generator=g) * 0.5).bfloat16()
+    qc, kc, vc = (t.cuda().transpose(1, 2) for t in (qp, kp, vp))
+    out = ops.attention(qc, kc, vc, start.cuda(), ln.cuda(), D ** -0.5, mbl, algo=TC).float().cpu()
+    T = sum(bl)
+    rows = torch.tensor([[T - 2, T - 1]], dtype=torch.int32)
+    mass, logits = ops.doc_scores(qc, kc, start.cuda(), ln.cuda(), rows.cuda(), D ** -0.5)
+    M, Hp = len(bl), 256
+    mask = H_.ragged_mask(1, M, Hp, [bl])
+    idx = H_.packed_to_padded(bl, Hp)
+    qd = torch.zeros(1, M * Hp, N, D); kd = torch.zeros(1, M * Hp, Nk, D); vd = torch.zeros(1, M * Hp, Nk, D)
+    qd[0, idx], kd[0, idx], vd[0, idx] = qp[0, :T].float(), kp[0, :T].float(), vp[0, :T].float()
+    ref = orc.attention_blocked(qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2), mask, D ** -0.5)
+    assert (out[0, :T] - ref[0, idx].float()).abs().max().item() < 2e-2
+    assert out[0, T:].abs().sum().item() == 0
+    sig = torch.tensor([[M * Hp - 2, M * Hp - 1]])
+    exact = orc.doc_mass(qd.transpose(1, 2), kd.transpose(1, 2), mask, D ** -0.5, sig)
+    assert torch.allclose(mass.cpu().double(), exact, rtol=2e-3, atol=1e-7)
+
+
+def test_full_size_ragged_long_list_properties():
+    """BASELINE config 5 geometry at full size (500 documents of 32..256 tokens, ~72k tokens, one
+    prompt): size-independent properties instead of an oracle run --
+    (1) the tensor-core and CUDA-core kernels agree; (2) each row's document masses sum to one;
+    (3) swapping two documents (moving their Q/K/V rows) moves their outputs and scores with them."""
+    N, Nk, D = 32, 8, 128
+    bl = _ragged_prompt(500, seed=5)
+    start, ln, S, mbl = H_.packed_spans([bl])
+    T = sum(bl)
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(5)
+    mk = lambda h: (torch.randn(1, S, h, D, generator=g, device=dev) * 0.5).bfloat16()
+    q, k, v = mk(N), mk(Nk), mk(Nk)
+    sc, lc = start.cuda(), ln.cuda()
+    run = lambda qq, kk, vv, s_, l_, algo: ops.attention(qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                                        s_, l_, D ** -0.5, mbl, algo=algo)
+    o_tc = run(q, k, v, sc, lc, TC)
+    o_si = run(q, k, v, sc, lc, SIMT)
+    assert (o_tc.float() - o_si.float())[0, :T].abs().max().item() < 2e-2
+    rows = torch.tensor([[T - 2, T - 1]], dtype=torch.int32, device=dev)
+    mass, logits = ops.doc_scores(q.transpose(1, 2), k.transpose(1, 2), sc, lc, rows, D ** -0.5)
+    assert torch.allclose(mass.sum(-1), torch.ones_like(mass.sum(-1)), atol=1e-4)
+    # swap documents 7 and 311 (block indices 8 and 312)
+    i, j = 8, 312
+    order = list(range(len(bl)))
+    order[i], order[j] = order[j], order[i]
+    bl2 = [bl[m] for m in order]
+    start2, ln2, S2, _ = H_.packed_spans([bl2])
+    assert S2 == S
+    perm = torch.cat([torch.arange(int(start[0, m]), int(start[0, m]) + bl[m]) for m in order]).to(dev)
+    q2, k2, v2 = (torch.zeros_like(t) for t in (q, k, v))
+    q2[0, :T], k2[0, :T], v2[0, :T] = q[0, perm], k[0, perm], v[0, perm]
+    o2 = run(q2, k2, v2, start2.cuda(), ln2.cuda(), TC)
+    assert (o2[0, :T].float() - o_tc[0, perm].float()).abs().max().item() < 1e-2
+    mass2, _ = ops.doc_scores(q2.transpose(1, 2), k2.transpose(1, 2), start2.cuda(), ln2.cuda(), rows, D ** -0.5)
+    docs = [m - 1 for m in order[1:-1]]
+    assert torch.allclose(mass2, mass[..., docs], rtol=1e-3, atol=1e-7)
