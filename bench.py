@@ -346,7 +346,11 @@ def run_ours(args):
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": "attn_tc_kernel" if args.algo != "simt" else "attn_simt_kernel",
                      "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                     "frac": achieved / pk["bf16_tflops_sustained"], "traffic": None, "peak_source": pk["source"],
+                     "frac": achieved / pk["bf16_tflops_sustained"],
+                     # dram__bytes_read+write of one ncu capture on 2 prompts of this geometry (profiles/),
+                     # 476.3 MB per prompt, scaled to the prompts of one launch (traffic grows with prompts)
+                     "traffic": 476.3e6 * micro if args.docs == 100 and args.algo != "simt" else None,
+                     "peak_source": pk["source"],
                      "flops_exact_per_launch": f_exact * micro, "launch_ms": attn_avg_s * 1e3,
                      "live_tile_tflops": live, "live_tile_frac": live / pk["bf16_tflops_sustained"],
                      "exact_over_tile": f_exact / f_tile,
@@ -355,7 +359,7 @@ def run_ours(args):
                      "launches_timed": len(attn_ms)},
         "score_epilogue": {"bound": "hbm", "achieved": score_bytes(bl) * micro / sc_avg_s / 1e9, "peak": pk["hbm_gbs"],
                            "unit": "GB/s", "frac": score_bytes(bl) * micro / sc_avg_s / 1e9 / pk["hbm_gbs"],
-                           "launch_ms": sc_avg_s * 1e3, "note": "two launches (partials + finalize) timed together"},
+                           "launch_ms": sc_avg_s * 1e3, "note": "three launches (partials, per-row finalize, logits) timed together"},
         "clocks": clk.summary(),
     }
     if world == 1 and not args.no_cpu_baseline:

@@ -23,8 +23,8 @@
 // O stays in TMEM across the key tiles of an item; softmax is base-2, online, with a lazy
 // rescale (O is only touched when the running max grows by more than 2^8).
 //
-// Shared memory 225 KB: Q 2x32 KB, P 2x16 KB, K/V ring 4x32 KB.  TMEM: 2 x (S 64 + O 128)
-// columns.  No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the
+// Shared memory 225 KB: Q 2x32 KB, P 2x16 KB, K/V ring 4x32 KB.  TMEM: 2 x (S 2x64 + O 128)
+// columns: S is double buffered per chain so that the next QK^T runs under the current softmax.  No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the
 // thread records a code in the caller's status word, stops waiting and runs to the normal exit.
 #include <cuda.h>
 
@@ -94,21 +94,21 @@ constexpr uint32_t kOffKV = kOffP + 2 * kPBytes;
 constexpr uint32_t kOffBar = kOffKV + kStages * kStageBytes;
 constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;  // barriers + slack for the 1024-byte round-up
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kChainCols = 192;  // per chain: S [0,64) then O [64,192)
-constexpr uint32_t kColO = 64;
+constexpr uint32_t kChainCols = 256;  // per chain: S buffers [0,64) and [64,128), then O [128,256)
+constexpr uint32_t kColO = 128;
 constexpr float kLazy = 8.f;
 constexpr uint32_t kWaitBudget = 1u << 18;
 
 enum {
   kQFull = 0,    // +chain  TMA -> MMA: Q tile landed
   kQFree = 2,    // +chain  MMA -> TMA: every QK^T of the item has read Q
-  kSFull = 4,    // +chain  MMA -> softmax: S tile complete
-  kPFull = 6,    // +chain  softmax -> MMA: P in shared memory, S consumed (128 arrivals)
-  kPVDone = 8,   // +chain  MMA -> softmax: P V of a tile complete
-  kOFree = 10,   // +chain  softmax -> MMA: O read out of TMEM (128 arrivals)
-  kKVFull = 12,  // +stage  TMA -> MMA
-  kKVFree = 16,  // +stage  MMA -> TMA
-  kNumBars = 20
+  kSFull = 4,    // +2*chain+buffer  MMA -> softmax: S tile complete (S is double buffered per chain)
+  kPFull = 8,    // +chain  softmax -> MMA: P in shared memory, S consumed (128 arrivals)
+  kPVDone = 10,  // +chain  MMA -> softmax: P V of a tile complete
+  kOFree = 12,   // +chain  softmax -> MMA: O read out of TMEM (128 arrivals)
+  kKVFull = 14,  // +stage  TMA -> MMA
+  kKVFree = 18,  // +stage  MMA -> TMA
+  kNumBars = 22
 };
 
 struct TcArgs {
@@ -123,6 +123,7 @@ struct TcArgs {
   int n_split;      // key chunks of the query block's context (1 = no split)
   int lq_max;       // rows per (prompt, head) in the partial buffers (= max_block_len)
   int pairs;        // row-tile pairs per block (covers max_block_len)
+  int o_align32;    // output rows are 32-byte aligned (enables 32-byte stores)
   int total_items;
   float* part_o;    // [B, N, lq_max, n_split, 128] un-normalised partial outputs
   float2* part_ml;  // [B, N, lq_max, n_split] (running max in log2 units, sum)
@@ -139,34 +140,57 @@ struct Item {
   bool split, valid;
 };
 
+// Block spans an item needs, fetched one item ahead of their use: decoding is two dependent
+// global-memory round trips, which would otherwise sit on every role's critical path.
+struct ItemRaw {
+  int m, chunk, p, b, g;
+  int start, len;      // span of block m
+  int s0, l0;          // span of block 0 (the prefix)
+  int s2, l2;          // span of block M-2 (end of the query block's context)
+};
+
 // Work list order: query-block chunks first (longest), then blocks M-2 .. 0.
-__device__ __forceinline__ Item decode_item(const TcArgs& a, int idx) {
-  Item it;
+__device__ __forceinline__ ItemRaw load_item(const TcArgs& a, int idx) {
+  ItemRaw r;
+  if (idx >= a.total_items) idx = a.total_items - 1;  // prefetch past the end: harmless reload
   const int nbg = a.B * a.Nk;
-  const int TOK = BM >> a.g_shift;
   const int sec1 = nbg * a.n_split * a.pairs;
-  int p, bg;
+  int bg;
   if (idx < sec1) {
-    p = idx / (nbg * a.n_split);
-    const int r = idx % (nbg * a.n_split);
-    it.chunk = r / nbg;
-    bg = r % nbg;
-    it.m = a.M - 1;
+    r.p = idx / (nbg * a.n_split);
+    const int q = idx % (nbg * a.n_split);
+    r.chunk = q / nbg;
+    bg = q % nbg;
+    r.m = a.M - 1;
   } else {
     const int i2 = idx - sec1;
-    p = i2 / (nbg * (a.M - 1));
-    const int r = i2 % (nbg * (a.M - 1));
-    it.m = a.M - 2 - r / nbg;
-    bg = r % nbg;
-    it.chunk = 0;
+    r.p = i2 / (nbg * (a.M - 1));
+    const int q = i2 % (nbg * (a.M - 1));
+    r.m = a.M - 2 - q / nbg;
+    bg = q % nbg;
+    r.chunk = 0;
   }
-  it.b = bg / a.Nk;
-  it.g = bg % a.Nk;
-  const int32_t* bs = a.blk_start + (size_t)it.b * a.M;
-  const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
-  it.start = bs[it.m];
-  it.len = bl[it.m];
-  it.t0[0] = 2 * p * TOK;
+  r.b = bg / a.Nk;
+  r.g = bg % a.Nk;
+  const int32_t* bs = a.blk_start + (size_t)r.b * a.M;
+  const int32_t* bl = a.blk_len + (size_t)r.b * a.M;
+  const int m2 = a.M >= 2 ? a.M - 2 : 0;
+  r.start = bs[r.m];
+  r.len = bl[r.m];
+  r.s0 = bs[0];
+  r.l0 = bl[0];
+  r.s2 = bs[m2];
+  r.l2 = bl[m2];
+  return r;
+}
+
+__device__ __forceinline__ Item decode_item(const TcArgs& a, const ItemRaw& r) {
+  Item it;
+  const int TOK = BM >> a.g_shift;
+  it.b = r.b; it.g = r.g; it.m = r.m; it.chunk = r.chunk;
+  it.start = r.start;
+  it.len = r.len;
+  it.t0[0] = 2 * r.p * TOK;
   it.t0[1] = it.t0[0] + TOK;
   it.valid = it.t0[0] < it.len;
   it.split = it.m == a.M - 1 && a.n_split > 1;
@@ -175,8 +199,8 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, int idx) {
   it.n_x[0] = it.n_x[1] = 0;
   if (!it.valid) return it;
   if (it.m > 0) {
-    it.ctx_lo = bs[0];
-    it.ctx_hi = (it.m < a.M - 1) ? bs[0] + bl[0] : bs[a.M - 2] + bl[a.M - 2];
+    it.ctx_lo = r.s0;
+    it.ctx_hi = (it.m < a.M - 1) ? r.s0 + r.l0 : r.s2 + r.l2;
   }
   const bool on1 = it.t0[1] < it.len;
   it.own_n = min(it.len, (on1 ? it.t0[1] : it.t0[0]) + TOK);
@@ -294,10 +318,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   if (warp == 8) {
     // =============================== TMA producer ===============================================
-    if (lane == 0) {
+    // The whole warp runs the control flow (so addresses and counters stay warp-uniform); one lane
+    // issues the copies.
+    {
+      const bool leader = lane == 0;
       uint32_t kv_cnt = 0, q_loads[2] = {0, 0};
+      ItemRaw raw_next = load_item(a, blockIdx.x);
       for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
-        const Item it = decode_item(a, idx);
+        const ItemRaw raw = raw_next;
+        raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
+        const Item it = decode_item(a, raw);
         if (!it.valid) continue;
         for (int x = 0; x < 2; ++x) {
           if (it.n_x[x] == 0) continue;
@@ -305,11 +335,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           long long tc_t_ = clock64();
 #endif
           if (q_loads[x] > 0) wait(kQFree + x, q_loads[x] - 1, 10 + x);
-          TC_ACC(24, true);  // producer: wait Q free
+          TC_ACC(24, leader);  // producer: wait Q free
           const uint32_t dst = sbase + kOffQ + (uint32_t)x * kQBytes;
-          ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
-          ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, it.g * G, it.start + it.t0[x], it.b);
-          ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, it.g * G, it.start + it.t0[x], it.b);
+          if (leader) {
+            ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
+            ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, it.g * G, it.start + it.t0[x], it.b);
+            ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, it.g * G, it.start + it.t0[x], it.b);
+          }
           ++q_loads[x];
         }
         for (int j = 0; j < it.n_tiles; ++j) {
@@ -320,21 +352,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           long long tc_t_ = clock64();
 #endif
           if (use > 0) wait(kKVFree + st, use - 1, 12);
-          TC_ACC(25, true);  // producer: wait KV stage free
+          TC_ACC(25, leader);  // producer: wait KV stage free
           const uint32_t dst = sbase + kOffKV + st * kStageBytes;
-          ptx::mbar_expect_tx(bar(kKVFull + st), kStageBytes);
-          ptx::tma_load_4d(dst, &tmK, bar(kKVFull + st), 0, it.g, lo, it.b);
-          ptx::tma_load_4d(dst + BN * 128, &tmK, bar(kKVFull + st), 64, it.g, lo, it.b);
-          ptx::tma_load_4d(dst + kKBytes, &tmV, bar(kKVFull + st), 0, it.g, lo, it.b);
-          ptx::tma_load_4d(dst + kKBytes + BN * 128, &tmV, bar(kKVFull + st), 64, it.g, lo, it.b);
+          if (leader) {
+            ptx::mbar_expect_tx(bar(kKVFull + st), kStageBytes);
+            ptx::tma_load_4d(dst, &tmK, bar(kKVFull + st), 0, it.g, lo, it.b);
+            ptx::tma_load_4d(dst + BN * 128, &tmK, bar(kKVFull + st), 64, it.g, lo, it.b);
+            ptx::tma_load_4d(dst + kKBytes, &tmV, bar(kKVFull + st), 0, it.g, lo, it.b);
+            ptx::tma_load_4d(dst + kKBytes + BN * 128, &tmV, bar(kKVFull + st), 64, it.g, lo, it.b);
+          }
           ++kv_cnt;
         }
       }
     }
   } else if (warp == 9) {
     // =============================== MMA issuer =================================================
-    if (lane == 0) {
-      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0};
+    // Whole-warp control flow, one issuing lane (always the same one: tcgen05.commit tracks the
+    // MMAs of the thread that executes it).
+    {
+      const bool leader = lane == 0;
+      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0}, s_cnt[2] = {0, 0};
       // Descriptors are built once: every operand buffer has a fixed address, and stepping along K
       // or to another ring stage only adds a constant to the 16-byte-unit start-address field.
       const uint32_t idesc_pv = ptx::idesc_bf16(BM, HD, 0, 1);
@@ -347,28 +384,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t idesc = idesc_qk0 | ((uint32_t)((nk + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
         const uint64_t ad = q_desc0 + (uint64_t)((uint32_t)x * (kQBytes >> 4));
         const uint64_t bd = k_desc0 + (uint64_t)(st * (kStageBytes >> 4));
-        const uint32_t d = tmem + (uint32_t)x * kChainCols;
+        const uint32_t buf = s_cnt[x] & 1u;
+        const uint32_t d = tmem + (uint32_t)x * kChainCols + buf * BN;
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
-          const uint32_t boff = (uint32_t)(ks >> 2) * ((BN * 128) >> 4) + (uint32_t)(ks & 3) * 2;
-          ptx::mma_ss(d, ad + aoff, bd + boff, idesc, ks > 0);
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
+            const uint32_t boff = (uint32_t)(ks >> 2) * ((BN * 128) >> 4) + (uint32_t)(ks & 3) * 2;
+            ptx::mma_ss(d, ad + aoff, bd + boff, idesc, ks > 0);
+          }
+          ptx::mma_commit(bar(kSFull + 2 * x + (int)buf));
+          if (last) ptx::mma_commit(bar(kQFree + x));  // last read of this chain's Q tile
         }
-        ptx::mma_commit(bar(kSFull + x));
-        if (last) ptx::mma_commit(bar(kQFree + x));  // last read of this chain's Q tile
+        ++s_cnt[x];
       };
       auto issue_pv = [&](int x, int nk, bool first, uint32_t st) {
         const uint64_t ad = p_desc0 + (uint64_t)((uint32_t)x * (kPBytes >> 4));
         const uint64_t bd = v_desc0 + (uint64_t)(st * (kStageBytes >> 4));
         const uint32_t d = tmem + (uint32_t)x * kChainCols + kColO;
         const int ksteps = (nk + 15) >> 4;
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks)
-          if (ks < ksteps) ptx::mma_ss(d, ad + (uint32_t)ks * 2, bd + (uint32_t)ks * ((16 * 128) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
-        ptx::mma_commit(bar(kPVDone + x));
+          for (int ks = 0; ks < BN / 16; ++ks)
+            if (ks < ksteps) ptx::mma_ss(d, ad + (uint32_t)ks * 2, bd + (uint32_t)ks * ((16 * 128) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
+          ptx::mma_commit(bar(kPVDone + x));
+        }
       };
+      ItemRaw raw_next = load_item(a, blockIdx.x);
       for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
-        const Item it = decode_item(a, idx);
+        const ItemRaw raw = raw_next;
+        raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
+        const Item it = decode_item(a, raw);
         if (!it.valid) continue;
         const int n0 = it.n_x[0], n1 = it.n_x[1];
 #ifdef BRK_TC_TIMING
@@ -377,7 +423,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
         for (int x = 0; x < 2; ++x)
           if ((x == 0 ? n0 : n1) > 0) { wait(kQFull + x, q_uses[x], 20 + x); ++q_uses[x]; }
-        TC_ACC(16, true);  // MMA: wait Q
+        TC_ACC(16, leader);  // MMA: wait Q
         int kv_waited = -1;
         auto need_kv = [&](int j) {
           if (kv_waited >= j) return;
@@ -391,7 +437,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           return nk;
         };
         need_kv(0);
-        TC_ACC(17, true);  // MMA: wait first KV
+        TC_ACC(17, leader);  // MMA: wait first KV
         ptx::tc_fence_after_sync();
         {
           const int nk = tile_nk(0);
@@ -405,28 +451,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int j = 0; j < it.n_tiles; ++j) {
           const uint32_t st = (kv_cnt + (uint32_t)j) % kStages;
           const int nk_next = (j + 1 < it.n_tiles) ? tile_nk(j + 1) : 0;
+          // next tile's QK^T first: it lands in the chain's other S buffer (whose last reader, the
+          // softmax of tile j-1, has already signalled) and runs under the softmax of tile j
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
             const int nx = x == 0 ? n0 : n1;
-            if (j >= nx) continue;
-            TC_ACC(18, true);  // MMA: issue work
-            wait(kPFull + x, p_seen[x], 24 + x);
-            ++p_seen[x];
-            TC_ACC(19, true);  // MMA: wait P
-            if (j == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
-            TC_ACC(20, true);  // MMA: wait O free
-            ptx::tc_fence_after_sync();
-            issue_pv(x, nk_cur, j == 0, st);
             if (j + 1 < nx) {
-              TC_ACC(18, true);
+              TC_ACC(18, leader);
               need_kv(j + 1);
-              TC_ACC(21, true);  // MMA: wait next KV
+              TC_ACC(21, leader);  // MMA: wait next KV
               ptx::tc_fence_after_sync();
               issue_qk(x, nk_next, j + 2 == nx, (kv_cnt + (uint32_t)j + 1) % kStages);
             }
           }
-          ptx::mma_commit(bar(kKVFree + st));  // both chains' MMAs on this stage are queued
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int nx = x == 0 ? n0 : n1;
+            if (j >= nx) continue;
+            TC_ACC(18, leader);  // MMA: issue work
+            wait(kPFull + x, p_seen[x], 24 + x);
+            ++p_seen[x];
+            TC_ACC(19, leader);  // MMA: wait P
+            if (j == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
+            TC_ACC(20, leader);  // MMA: wait O free
+            ptx::tc_fence_after_sync();
+            issue_pv(x, nk_cur, j == 0, st);
+          }
+          if (leader) ptx::mma_commit(bar(kKVFree + st));  // both chains' MMAs on this stage are queued
           nk_cur = nk_next;
+          TC_ACC(18, leader);
         }
         kv_cnt += (uint32_t)it.n_tiles;
 #pragma unroll
@@ -441,8 +494,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)x * kChainCols;
     uint8_t* pbuf = smem + kOffP + (uint32_t)x * kPBytes;
     uint32_t s_seen = 0, pv_seen = 0;
+    ItemRaw raw_next = load_item(a, blockIdx.x);
     for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
-      const Item it = decode_item(a, idx);
+      const ItemRaw raw = raw_next;
+      raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
+      const Item it = decode_item(a, raw);
       if (!it.valid || it.n_x[x] == 0) continue;
       const int32_t* bs = a.blk_start + (size_t)it.b * a.M;
       const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
@@ -466,7 +522,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         int nk, own_off; bool own;
         const int lo = tile_lo(it, j, nk, own, own_off);
         TC_ACC(0, tc_me);  // decode / loop overhead
-        wait(kSFull + x, s_seen, 30 + x);
+        const uint32_t buf = s_seen & 1u;
+        wait(kSFull + 2 * x + (int)buf, s_seen >> 1, 30 + x);
         ++s_seen;
         TC_ACC(1, tc_me);  // wait S
         ptx::tc_fence_after_sync();
@@ -475,8 +532,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         {
           uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
           uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
-          ptx::tmem_ld32(tmem_lane, lo32);
-          ptx::tmem_ld32(tmem_lane + 32, hi32);
+          ptx::tmem_ld32(tmem_lane + buf * BN, lo32);
+          ptx::tmem_ld32(tmem_lane + buf * BN + 32, hi32);
           ptx::tmem_wait_ld();
         }
         TC_ACC(2, tc_me);  // TMEM load of S
@@ -486,7 +543,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
         if (!need_mask) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+          for (int c = 0; c < 64; c += 2)
+            mx4[(c >> 1) & 3] = ptx::max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
         } else {
           int lim = nk;  // columns [0, lim) are visible to this row
           if (own) lim = max(0, min(nk, tok - own_off + 1));
@@ -509,17 +567,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
         const float corr = ptx::ex2(m_run - m_ref);  // 1 when unchanged, 0 on the first visible tile
         const float neg_ref = -m_ref;
-        float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+        // p = 2^(s*scale - m) with packed fp32x2 arithmetic.  Every second pair of exponentials is
+        // evaluated on the FMA pipe: the special-function unit (16 results per clock per SM) would
+        // otherwise bound the whole kernel.
+        const ptx::f32x2 sc2 = ptx::pack2(a.scale_log2, a.scale_log2), nr2 = ptx::pack2(neg_ref, neg_ref);
+        ptx::f32x2 ps2[2] = {0ull, 0ull};
         uint32_t pk[32];
 #pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_ref));
-          const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_ref));
-          ps4[(c >> 1) & 3] += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+        for (int c = 0; c < 64; c += 4) {
+          const ptx::f32x2 t01 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nr2);
+          const ptx::f32x2 t23 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nr2);
+          float t0, t1, p2, p3;
+          ptx::unpack2(t01, t0, t1);
+          const float p0 = ptx::ex2(t0), p1 = ptx::ex2(t1);
+          const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
+          ptx::unpack2(p23, p2, p3);
+          ps2[0] = ptx::add2(ps2[0], ptx::pack2(p0, p1));
+          ps2[1] = ptx::add2(ps2[1], p23);
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+          pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+          pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
         }
-        l_run = l_run * corr + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+        float s0, s1, s2, s3;
+        ptx::unpack2(ps2[0], s0, s1);
+        ptx::unpack2(ps2[1], s2, s3);
+        l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
         const bool changed = m_new != m_run;
         m_run = m_new;
         TC_ACC(3, tc_me);  // softmax math
@@ -584,48 +656,40 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ptx::mbar_arrive(bar(kOFree + x));
         if (wr) a.part_ml[prow] = make_float2(m_run, l_run);
       } else {
-        // O / l -> bf16 -> staging in this chain's P buffer, one 64-wide half of D at a time ->
-        // coalesced 16-byte stores
+        // O / l -> bf16, stored straight from registers: each thread owns one 256-byte output row
+        // and writes it as eight 32-byte (full-sector) stores, or sixteen 16-byte ones if the
+        // output is only 16-byte aligned.
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb;
-        const int wt = tid & 127;
+        __nv_bfloat16* orow_ptr = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb +
+                                  (int64_t)(it.start + tok) * a.o.ss + (int64_t)n * a.o.sh;
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll 1
-          for (int cc = 0; cc < 2; ++cc) {
-            uint32_t orow[32];
-            ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)(2 * h + cc) * 32, orow);
-            ptx::tmem_wait_ld();
-            uint8_t* srow = pbuf + (uint32_t)r * 128;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint32_t w[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(orow[q4 * 8 + 2 * i]) * inv,
-                                                          __uint_as_float(orow[q4 * 8 + 2 * i + 1]) * inv);
-                w[i] = *reinterpret_cast<uint32_t*>(&hh);
-              }
-              const int c16 = cc * 4 + q4;
-              *reinterpret_cast<uint4*>(srow + ((c16 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
-          if (h == 1) {  // O is out of TMEM: the next item's first P V may overwrite it
+        for (int ch = 0; ch < HD / 32; ++ch) {
+          uint32_t orow[32];
+          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+          ptx::tmem_wait_ld();
+          if (ch == HD / 32 - 1) {  // O is out of TMEM: the next item's first P V may overwrite it
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(bar(kOFree + x));
           }
-          ptx::named_bar_sync(1 + x, 128);
-          for (int itr = 0; itr < 8; ++itr) {
-            const int rr = itr * 16 + (wt >> 3), piece = wt & 7;
-            const int rtok = it.t0[x] + (rr >> a.g_shift);
-            if (rtok < it.len) {
-              const uint8_t* src = pbuf + (uint32_t)rr * 128 + ((piece ^ (rr & 7)) << 4);
-              __nv_bfloat16* dst = ob + (int64_t)(it.start + rtok) * a.o.ss +
-                                   (int64_t)(it.g * G + (rr & (G - 1))) * a.o.sh + h * 64 + piece * 8;
-              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+          if (active) {
+#pragma unroll
+            for (int q8 = 0; q8 < 2; ++q8) {
+              uint32_t w[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(orow[q8 * 16 + 2 * i]) * inv,
+                                                          __uint_as_float(orow[q8 * 16 + 2 * i + 1]) * inv);
+                w[i] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              __nv_bfloat16* dst = orow_ptr + ch * 32 + q8 * 16;
+              if (a.o_align32) {
+                ptx::st_global_v8(dst, w);
+              } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+              }
             }
           }
-          ptx::named_bar_sync(1 + x, 128);
         }
         if (active && a.lse != nullptr)
           a.lse[((int64_t)it.b * a.N + n) * a.S + it.start + tok] = (m_run + log2f(l_run)) * 0.6931471805599453f;
@@ -745,6 +809,7 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   a.n_split = ns;
   a.lq_max = p.max_block_len;
   a.pairs = pairs;
+  a.o_align32 = (((uintptr_t)p.o.ptr & 31) == 0 && p.o.stride_b % 16 == 0 && p.o.stride_h % 16 == 0 && p.o.stride_s % 16 == 0) ? 1 : 0;
   a.total_items = (int)total_items;
   const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
   a.part_o = ns > 1 ? reinterpret_cast<float*>(ws) : nullptr;

@@ -17,7 +17,7 @@
 namespace brk {
 namespace {
 
-constexpr int kThreads = 128;
+constexpr int kThreads = 160;  // five warps: a 160-token document is one pass
 constexpr int kRowBatch = 8;  // signal rows accumulated per pass over a key
 
 struct ScoreArgs {

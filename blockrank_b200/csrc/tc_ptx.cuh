@@ -53,6 +53,62 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// ---- packed fp32x2 arithmetic (two lanes per instruction) and 3-input max ---------------------
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x for two values on the FMA/ALU pipes (no special-function unit): Cody-Waite split
+// x = n + f with f in [-0.5, 0.5], a minimax cubic for 2^f (relative error 7.5e-5, far below bf16
+// resolution), and n added into the exponent field.  Inputs below -126 (including -inf) give
+// 2^-126, i.e. zero for every purpose here.
+__device__ __forceinline__ f32x2 ex2_poly2(f32x2 x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const f32x2 magic = pack2(12582912.f, 12582912.f);      // 1.5 * 2^23: adding it rounds to nearest integer
+  const f32x2 neg_magic = pack2(-12582912.f, -12582912.f);
+  const f32x2 neg_one = pack2(-1.f, -1.f);
+  const f32x2 r = add2(x2, magic);
+  const f32x2 f = fma2(add2(r, neg_magic), neg_one, x2);  // x - round(x)
+  f32x2 p = fma2(f, pack2(0.05517148599f, 0.05517148599f), pack2(0.24261091650f, 0.24261091650f));
+  p = fma2(p, f, pack2(0.69326096773f, 0.69326096773f));
+  p = fma2(p, f, pack2(0.99992805719f, 0.99992805719f));
+  float p0, p1, r0, r1;
+  unpack2(p, p0, p1);
+  unpack2(r, r0, r1);
+  return pack2(__int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23)),
+               __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23)));
+}
+
+// 32-byte global store (eight 32-bit words); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 // ---- fences ---------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
