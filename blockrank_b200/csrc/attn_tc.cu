@@ -19,12 +19,14 @@
 //   warps 0-3 / 4-7  softmax + epilogue of chain 0 / 1 (thread = row = TMEM lane)
 //   warp 8           TMA producer: Q tiles and a 4-stage K/V ring, running ahead across items
 //   warp 9           MMA issuer: S = Q K^T (both operands K-major, 128B swizzle) and O += P V
-//                    (P from swizzled shared memory, V as the MN-major B operand)
+//                    (P read from tensor memory, V as the MN-major B operand)
 // O stays in TMEM across the key tiles of an item; softmax is base-2, online, with a lazy
 // rescale (O is only touched when the running max grows by more than 2^8).
 //
-// Shared memory 225 KB: Q 2x32 KB, P 2x16 KB, K/V ring 4x32 KB.  TMEM: 2 x (S 2x64 + O 128)
-// columns: S is double buffered per chain so that the next QK^T runs under the current softmax.  No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the
+// Shared memory 225 KB: Q 2x32 KB, K/V ring 5x32 KB.  TMEM: 2 x (S 2x64 + O 128) columns: S is
+// double buffered per chain so that the next QK^T runs under the current softmax, and P (bf16,
+// two keys per 32-bit column) overwrites the first half of the S buffer it was computed from, so
+// the probabilities never touch shared memory.  No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the
 // thread records a code in the caller's status word, stops waiting and runs to the normal exit.
 #include <cuda.h>
 
@@ -64,33 +66,19 @@ int make_tmap_bf16(CUtensorMap* out, const void* ptr, int D, int heads, int S, i
   return BRK_OK;
 }
 
-#ifdef BRK_TC_TIMING
-// Development aid: per-phase cycle counters (accumulated by one thread per role over all CTAs).
-__device__ unsigned long long g_tc_cycles[32];
-#define TC_T0() const long long tc_t0_ = clock64()
-#define TC_ACC(slot, pred)                                                          \
-  do {                                                                              \
-    if (pred) atomicAdd(&g_tc_cycles[slot], (unsigned long long)(clock64() - tc_t_)); \
-    tc_t_ = clock64();                                                              \
-  } while (0)
-#else
-#define TC_ACC(slot, pred) do { } while (0)
-#endif
 
 namespace {
 
 constexpr int BM = 128;  // query rows (token, head) per row tile
 constexpr int BN = 64;   // keys per tile
 constexpr int HD = 128;  // head dim
-constexpr int kStages = 4;
+constexpr int kStages = 5;
 constexpr int kThreads = 320;
 constexpr uint32_t kQBytes = 2 * BM * 128;  // two 64-wide halves of D
 constexpr uint32_t kKBytes = 2 * BN * 128;  // one K (or V) tile
 constexpr uint32_t kStageBytes = 2 * kKBytes;
-constexpr uint32_t kPBytes = BM * 128;
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffP = kOffQ + 2 * kQBytes;
-constexpr uint32_t kOffKV = kOffP + 2 * kPBytes;
+constexpr uint32_t kOffKV = kOffQ + 2 * kQBytes;
 constexpr uint32_t kOffBar = kOffKV + kStages * kStageBytes;
 constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;  // barriers + slack for the 1024-byte round-up
 constexpr uint32_t kTmemCols = 512;
@@ -103,12 +91,12 @@ enum {
   kQFull = 0,    // +chain  TMA -> MMA: Q tile landed
   kQFree = 2,    // +chain  MMA -> TMA: every QK^T of the item has read Q
   kSFull = 4,    // +2*chain+buffer  MMA -> softmax: S tile complete (S is double buffered per chain)
-  kPFull = 8,    // +chain  softmax -> MMA: P in shared memory, S consumed (128 arrivals)
+  kPFull = 8,    // +chain  softmax -> MMA: P written to tensor memory, S consumed (4 warp arrivals)
   kPVDone = 10,  // +chain  MMA -> softmax: P V of a tile complete
-  kOFree = 12,   // +chain  softmax -> MMA: O read out of TMEM (128 arrivals)
+  kOFree = 12,   // +chain  softmax -> MMA: O read out of TMEM (4 warp arrivals)
   kKVFull = 14,  // +stage  TMA -> MMA
-  kKVFree = 18,  // +stage  MMA -> TMA
-  kNumBars = 22
+  kKVFree = 14 + kStages,  // +stage  MMA -> TMA
+  kNumBars = 14 + 2 * kStages
 };
 
 struct TcArgs {
@@ -132,8 +120,11 @@ struct TcArgs {
 struct Item {
   int b, g, m, chunk;
   int start, len;        // span of block m
-  int t0[2];             // first token of each chain's row tile
-  int n_x[2];            // key tiles visible to each chain (a prefix of the item's tile list)
+  int t0_0, t0_1;        // first token of each chain's row tile
+  int n_0, n_1;          // key tiles visible to each chain (a prefix of the item's tile list)
+  // selected with a conditional move rather than an indexed array, so the item stays in registers
+  __device__ __forceinline__ int t0(int x) const { return x ? t0_1 : t0_0; }
+  __device__ __forceinline__ int n_x(int x) const { return x ? n_1 : n_0; }
   int ctx_lo, ctx_hi;    // context key range (slots)
   int n_ctx, j0;         // context tiles of the block, first tile of this item
   int n_tiles, own_n;
@@ -190,20 +181,20 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, const ItemRaw& r) {
   it.b = r.b; it.g = r.g; it.m = r.m; it.chunk = r.chunk;
   it.start = r.start;
   it.len = r.len;
-  it.t0[0] = 2 * r.p * TOK;
-  it.t0[1] = it.t0[0] + TOK;
-  it.valid = it.t0[0] < it.len;
+  it.t0_0 = 2 * r.p * TOK;
+  it.t0_1 = it.t0_0 + TOK;
+  it.valid = it.t0_0 < it.len;
   it.split = it.m == a.M - 1 && a.n_split > 1;
   it.ctx_lo = it.ctx_hi = 0;
   it.n_ctx = it.j0 = it.n_tiles = it.own_n = 0;
-  it.n_x[0] = it.n_x[1] = 0;
+  it.n_0 = it.n_1 = 0;
   if (!it.valid) return it;
   if (it.m > 0) {
     it.ctx_lo = r.s0;
     it.ctx_hi = (it.m < a.M - 1) ? r.s0 + r.l0 : r.s2 + r.l2;
   }
-  const bool on1 = it.t0[1] < it.len;
-  it.own_n = min(it.len, (on1 ? it.t0[1] : it.t0[0]) + TOK);
+  const bool on1 = it.t0_1 < it.len;
+  it.own_n = min(it.len, (on1 ? it.t0_1 : it.t0_0) + TOK);
   it.n_ctx = (it.ctx_hi - it.ctx_lo + BN - 1) / BN;
   const int own_tiles = (it.own_n + BN - 1) / BN;
   int j1 = it.n_ctx + own_tiles;
@@ -219,10 +210,13 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, const ItemRaw& r) {
     return it;
   }
   // own tiles visible to chain x: those starting at or before its last token
-  for (int x = 0; x < 2; ++x) {
-    if (x == 1 && !on1) break;
-    const int own_x = min(own_tiles, (min(it.len, it.t0[x] + TOK) + BN - 1) / BN);
-    it.n_x[x] = max(0, min(j1, it.n_ctx + own_x) - it.j0);
+  {
+    const int own_x = min(own_tiles, (min(it.len, it.t0_0 + TOK) + BN - 1) / BN);
+    it.n_0 = max(0, min(j1, it.n_ctx + own_x) - it.j0);
+  }
+  if (on1) {
+    const int own_x = min(own_tiles, (min(it.len, it.t0_1 + TOK) + BN - 1) / BN);
+    it.n_1 = max(0, min(j1, it.n_ctx + own_x) - it.j0);
   }
   return it;
 }
@@ -259,9 +253,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = a.G;
-#ifdef BRK_TC_TIMING
-  const long long tc_kernel_t0 = clock64();
-#endif
 
   // ---- padding slots of the output are written as zeros (gaps in front of / behind blocks) ----
   for (int gi = blockIdx.x; gi < a.B * (a.M + 1); gi += gridDim.x) {
@@ -291,7 +282,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (tid == 0) {
     for (int i = 0; i < kNumBars; ++i) {
       const bool many = (i >= kPFull && i < kPFull + 2) || (i >= kOFree && i < kOFree + 2);
-      ptx::mbar_init(bar(i), many ? 128u : 1u);
+      ptx::mbar_init(bar(i), many ? 4u : 1u);  // one arrival per softmax warp
     }
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmQ);
@@ -330,17 +321,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const Item it = decode_item(a, raw);
         if (!it.valid) continue;
         for (int x = 0; x < 2; ++x) {
-          if (it.n_x[x] == 0) continue;
-#ifdef BRK_TC_TIMING
-          long long tc_t_ = clock64();
-#endif
+          if (it.n_x(x) == 0) continue;
           if (q_loads[x] > 0) wait(kQFree + x, q_loads[x] - 1, 10 + x);
-          TC_ACC(24, leader);  // producer: wait Q free
           const uint32_t dst = sbase + kOffQ + (uint32_t)x * kQBytes;
           if (leader) {
             ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
-            ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, it.g * G, it.start + it.t0[x], it.b);
-            ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, it.g * G, it.start + it.t0[x], it.b);
+            ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, it.g * G, it.start + it.t0(x), it.b);
+            ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, it.g * G, it.start + it.t0(x), it.b);
           }
           ++q_loads[x];
         }
@@ -348,11 +335,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           int nk, own_off; bool own;
           const int lo = tile_lo(it, j, nk, own, own_off);
           const uint32_t st = kv_cnt % kStages, use = kv_cnt / kStages;
-#ifdef BRK_TC_TIMING
-          long long tc_t_ = clock64();
-#endif
           if (use > 0) wait(kKVFree + st, use - 1, 12);
-          TC_ACC(25, leader);  // producer: wait KV stage free
           const uint32_t dst = sbase + kOffKV + st * kStageBytes;
           if (leader) {
             ptx::mbar_expect_tx(bar(kKVFull + st), kStageBytes);
@@ -371,13 +354,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // MMAs of the thread that executes it).
     {
       const bool leader = lane == 0;
-      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0}, s_cnt[2] = {0, 0};
+      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0}, s_cnt[2] = {0, 0},
+               pv_cnt[2] = {0, 0};
       // Descriptors are built once: every operand buffer has a fixed address, and stepping along K
       // or to another ring stage only adds a constant to the 16-byte-unit start-address field.
       const uint32_t idesc_pv = ptx::idesc_bf16(BM, HD, 0, 1);
       const uint32_t idesc_qk0 = ptx::idesc_bf16(BM, 0, 0, 0);
       const uint64_t q_desc0 = ptx::smem_desc_sw128(sbase + kOffQ, 16, 1024);
-      const uint64_t p_desc0 = ptx::smem_desc_sw128(sbase + kOffP, 16, 1024);
       const uint64_t k_desc0 = ptx::smem_desc_sw128(sbase + kOffKV, 16, 1024);
       const uint64_t v_desc0 = ptx::smem_desc_sw128(sbase + kOffKV + kKBytes, BN * 128, 1024);
       auto issue_qk = [&](int x, int nk, bool last, uint32_t st) {
@@ -399,16 +382,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ++s_cnt[x];
       };
       auto issue_pv = [&](int x, int nk, bool first, uint32_t st) {
-        const uint64_t ad = p_desc0 + (uint64_t)((uint32_t)x * (kPBytes >> 4));
+        // P of this tile sits in the S buffer the tile was computed in (tiles alternate buffers)
+        const uint32_t pa = tmem + (uint32_t)x * kChainCols + (pv_cnt[x] & 1u) * BN;
         const uint64_t bd = v_desc0 + (uint64_t)(st * (kStageBytes >> 4));
         const uint32_t d = tmem + (uint32_t)x * kChainCols + kColO;
         const int ksteps = (nk + 15) >> 4;
         if (leader) {
 #pragma unroll
           for (int ks = 0; ks < BN / 16; ++ks)
-            if (ks < ksteps) ptx::mma_ss(d, ad + (uint32_t)ks * 2, bd + (uint32_t)ks * ((16 * 128) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
+            if (ks < ksteps) ptx::mma_ts(d, pa + (uint32_t)ks * 8, bd + (uint32_t)ks * ((16 * 128) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
           ptx::mma_commit(bar(kPVDone + x));
         }
+        ++pv_cnt[x];
       };
       ItemRaw raw_next = load_item(a, blockIdx.x);
       for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
@@ -416,14 +401,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
         const Item it = decode_item(a, raw);
         if (!it.valid) continue;
-        const int n0 = it.n_x[0], n1 = it.n_x[1];
-#ifdef BRK_TC_TIMING
-        long long tc_t_ = clock64();
-#endif
+        const int n0 = it.n_0, n1 = it.n_1;
 #pragma unroll
         for (int x = 0; x < 2; ++x)
           if ((x == 0 ? n0 : n1) > 0) { wait(kQFull + x, q_uses[x], 20 + x); ++q_uses[x]; }
-        TC_ACC(16, leader);  // MMA: wait Q
         int kv_waited = -1;
         auto need_kv = [&](int j) {
           if (kv_waited >= j) return;
@@ -437,7 +418,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           return nk;
         };
         need_kv(0);
-        TC_ACC(17, leader);  // MMA: wait first KV
         ptx::tc_fence_after_sync();
         {
           const int nk = tile_nk(0);
@@ -457,9 +437,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int x = 0; x < 2; ++x) {
             const int nx = x == 0 ? n0 : n1;
             if (j + 1 < nx) {
-              TC_ACC(18, leader);
               need_kv(j + 1);
-              TC_ACC(21, leader);  // MMA: wait next KV
               ptx::tc_fence_after_sync();
               issue_qk(x, nk_next, j + 2 == nx, (kv_cnt + (uint32_t)j + 1) % kStages);
             }
@@ -468,18 +446,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int x = 0; x < 2; ++x) {
             const int nx = x == 0 ? n0 : n1;
             if (j >= nx) continue;
-            TC_ACC(18, leader);  // MMA: issue work
             wait(kPFull + x, p_seen[x], 24 + x);
             ++p_seen[x];
-            TC_ACC(19, leader);  // MMA: wait P
             if (j == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
-            TC_ACC(20, leader);  // MMA: wait O free
             ptx::tc_fence_after_sync();
             issue_pv(x, nk_cur, j == 0, st);
           }
           if (leader) ptx::mma_commit(bar(kKVFree + st));  // both chains' MMAs on this stage are queued
           nk_cur = nk_next;
-          TC_ACC(18, leader);
         }
         kv_cnt += (uint32_t)it.n_tiles;
 #pragma unroll
@@ -492,17 +466,94 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int x = warp >> 2;
     const int r = tid & 127;  // row of the tile = TMEM lane
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)x * kChainCols;
-    uint8_t* pbuf = smem + kOffP + (uint32_t)x * kPBytes;
     uint32_t s_seen = 0, pv_seen = 0;
+
+    // What the drain of an item's output needs once its last key tile has been handed to the MMA.
+    // (Draining one tile late, behind the next item's first softmax tile, was measured slower.)
+    struct Pending {
+      bool any, split, write;
+      __nv_bfloat16* out_row;  // normal item: this thread's output row
+      float* lse_ptr;          // normal item: where the row's log-sum-exp goes (or null)
+      int64_t prow;            // split item: row of the partial buffers
+      float m_run, l_run;
+    } pend;
+    pend.any = false;
+
+    auto drain = [&]() {
+      wait(kPVDone + x, pv_seen, 34 + x);  // last P V of that item
+      ++pv_seen;
+      ptx::tc_fence_after_sync();
+      __syncwarp();
+      if (pend.split) {
+        // un-normalised partial (O, max, sum) of a key chunk; merged by attn_combine_kernel
+#pragma unroll 1
+        for (int ch = 0; ch < HD / 32; ++ch) {
+          uint32_t orow[32];
+          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+          ptx::tmem_wait_ld();
+          if (pend.write) {
+            float4* dst = reinterpret_cast<float4*>(a.part_o + pend.prow * HD + ch * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(orow[4 * i]), __uint_as_float(orow[4 * i + 1]),
+                                   __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
+        if (pend.write) a.part_ml[pend.prow] = make_float2(pend.m_run, pend.l_run);
+      } else {
+        // O / l -> bf16, stored straight from registers: each thread owns one 256-byte output row
+        // and writes it as eight 32-byte (full-sector) stores, or sixteen 16-byte ones if the
+        // output is only 16-byte aligned.
+        const float inv = pend.l_run > 0.f ? 1.f / pend.l_run : 0.f;
+        auto store32 = [&](const uint32_t (&orow)[32], int ch) {
+#pragma unroll
+          for (int q8 = 0; q8 < 2; ++q8) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(orow[q8 * 16 + 2 * i]) * inv,
+                                                        __uint_as_float(orow[q8 * 16 + 2 * i + 1]) * inv);
+              w[i] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            __nv_bfloat16* dst = pend.out_row + ch * 32 + q8 * 16;
+            if (a.o_align32) {
+              ptx::st_global_v8(dst, w);
+            } else {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+          }
+        };
+#pragma unroll 1
+        for (int ch = 0; ch < HD / 32; ++ch) {
+          uint32_t orow[32];
+          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+          ptx::tmem_wait_ld();
+          if (ch == HD / 32 - 1) {  // O is out of TMEM: the next item's first P V may overwrite it
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
+          }
+          if (pend.write) store32(orow, ch);
+        }
+        if (pend.write && pend.lse_ptr != nullptr)
+          *pend.lse_ptr = (pend.m_run + log2f(pend.l_run)) * 0.6931471805599453f;
+      }
+      pend.any = false;
+    };
+
     ItemRaw raw_next = load_item(a, blockIdx.x);
     for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
       const ItemRaw raw = raw_next;
       raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
       const Item it = decode_item(a, raw);
-      if (!it.valid || it.n_x[x] == 0) continue;
+      if (!it.valid || it.n_x(x) == 0) continue;
       const int32_t* bs = a.blk_start + (size_t)it.b * a.M;
       const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
-      const int tok = it.t0[x] + (r >> a.g_shift);
+      const int tok = it.t0(x) + (r >> a.g_shift);
       const int n = it.g * G + (r & (G - 1));
       const bool active = tok < it.len;
       bool ctx_check = false;  // the query block's context may contain padding slots
@@ -514,32 +565,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ctx_check = part != (it.ctx_hi - it.ctx_lo);
       }
       float m_run = -INFINITY, l_run = 0.f;
-#ifdef BRK_TC_TIMING
-      long long tc_t_ = clock64();
-      const bool tc_me = (tid == 0);
-#endif
-      for (int j = 0; j < it.n_x[x]; ++j) {
+      const int n_mine = it.n_x(x);
+      for (int j = 0; j < n_mine; ++j) {
         int nk, own_off; bool own;
         const int lo = tile_lo(it, j, nk, own, own_off);
-        TC_ACC(0, tc_me);  // decode / loop overhead
         const uint32_t buf = s_seen & 1u;
         wait(kSFull + 2 * x + (int)buf, s_seen >> 1, 30 + x);
         ++s_seen;
-        TC_ACC(1, tc_me);  // wait S
         ptx::tc_fence_after_sync();
         __syncwarp();
         uint32_t sr[64];
         {
           uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
           uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
+          {
           ptx::tmem_ld32(tmem_lane + buf * BN, lo32);
           ptx::tmem_ld32(tmem_lane + buf * BN + 32, hi32);
           ptx::tmem_wait_ld();
+          }
         }
-        TC_ACC(2, tc_me);  // TMEM load of S
         // Tiles fully inside the visible region need no per-element masking (the common case);
         // ragged tails, the causal diagonal and padded context ranges take the masked path.
-        const bool need_mask = nk < BN || (own && own_off + BN - 1 > it.t0[x]) || (!own && ctx_check);
+        const bool need_mask = nk < BN || (own && own_off + BN - 1 > it.t0(x)) || (!own && ctx_check);
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
         if (!need_mask) {
 #pragma unroll
@@ -594,12 +641,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
         const bool changed = m_new != m_run;
         m_run = m_new;
-        TC_ACC(3, tc_me);  // softmax math
 
         if (j > 0) {
-          wait(kPVDone + x, pv_seen, 32 + x);  // previous P V done: O stable, P buffer free
+          wait(kPVDone + x, pv_seen, 32 + x);  // previous P V done: O is stable
           ++pv_seen;
-          TC_ACC(4, tc_me);  // wait previous PV
           ptx::tc_fence_after_sync();
           if (__any_sync(0xffffffffu, changed)) {
 #pragma unroll 1
@@ -613,94 +658,36 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             ptx::tmem_wait_st();
           }
-          TC_ACC(5, tc_me);  // O rescale
         }
-        // P row -> shared memory in the K-major 128B-swizzled layout the MMA reads
+        // P row -> tensor memory, over the first 32 columns of the S buffer it came from
         {
-          uint8_t* prow = pbuf + (uint32_t)r * 128;
-#pragma unroll
-          for (int c16 = 0; c16 < 8; ++c16)
-            *reinterpret_cast<uint4*>(prow + ((c16 ^ (r & 7)) << 4)) =
-                make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
+        ptx::tmem_st32(tmem_lane + buf * BN, pk);
+        ptx::tmem_wait_st();
         }
-        ptx::fence_proxy_async_smem();
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(bar(kPFull + x));
-        TC_ACC(6, tc_me);  // P store + arrive
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kPFull + x));
       }
-
-      // ---- epilogue ----
-      wait(kPVDone + x, pv_seen, 34 + x);
-      ++pv_seen;
-      TC_ACC(7, tc_me);  // wait last PV
-      ptx::tc_fence_after_sync();
-      __syncwarp();
+      pend.any = true;
+      pend.split = it.split;
+      pend.m_run = m_run;
+      pend.l_run = l_run;
       if (it.split) {
-        // un-normalised partial (O, max, sum) of this key chunk; merged by attn_combine_kernel
-        const bool wr = active && tok < a.lq_max;
-        const int64_t prow = (((int64_t)it.b * a.N + n) * a.lq_max + tok) * a.n_split + it.chunk;
-#pragma unroll 1
-        for (int ch = 0; ch < HD / 32; ++ch) {
-          uint32_t orow[32];
-          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-          ptx::tmem_wait_ld();
-          if (wr) {
-            float4* dst = reinterpret_cast<float4*>(a.part_o + prow * HD + ch * 32);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              dst[i] = make_float4(__uint_as_float(orow[4 * i]), __uint_as_float(orow[4 * i + 1]),
-                                   __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
-          }
-        }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(bar(kOFree + x));
-        if (wr) a.part_ml[prow] = make_float2(m_run, l_run);
+        pend.write = active && tok < a.lq_max;
+        pend.prow = (((int64_t)it.b * a.N + n) * a.lq_max + tok) * a.n_split + it.chunk;
+        pend.out_row = nullptr;
+        pend.lse_ptr = nullptr;
       } else {
-        // O / l -> bf16, stored straight from registers: each thread owns one 256-byte output row
-        // and writes it as eight 32-byte (full-sector) stores, or sixteen 16-byte ones if the
-        // output is only 16-byte aligned.
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* orow_ptr = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb +
-                                  (int64_t)(it.start + tok) * a.o.ss + (int64_t)n * a.o.sh;
-#pragma unroll 1
-        for (int ch = 0; ch < HD / 32; ++ch) {
-          uint32_t orow[32];
-          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-          ptx::tmem_wait_ld();
-          if (ch == HD / 32 - 1) {  // O is out of TMEM: the next item's first P V may overwrite it
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(bar(kOFree + x));
-          }
-          if (active) {
-#pragma unroll
-            for (int q8 = 0; q8 < 2; ++q8) {
-              uint32_t w[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(orow[q8 * 16 + 2 * i]) * inv,
-                                                          __uint_as_float(orow[q8 * 16 + 2 * i + 1]) * inv);
-                w[i] = *reinterpret_cast<uint32_t*>(&hh);
-              }
-              __nv_bfloat16* dst = orow_ptr + ch * 32 + q8 * 16;
-              if (a.o_align32) {
-                ptx::st_global_v8(dst, w);
-              } else {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-              }
-            }
-          }
-        }
-        if (active && a.lse != nullptr)
-          a.lse[((int64_t)it.b * a.N + n) * a.S + it.start + tok] = (m_run + log2f(l_run)) * 0.6931471805599453f;
+        pend.write = active;
+        pend.prow = 0;
+        pend.out_row = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb +
+                       (int64_t)(it.start + tok) * a.o.ss + (int64_t)n * a.o.sh;
+        pend.lse_ptr = a.lse != nullptr ? a.lse + ((int64_t)it.b * a.N + n) * a.S + it.start + tok : nullptr;
       }
-      TC_ACC(8, tc_me);  // epilogue
+      drain();
     }
   }
 
-#ifdef BRK_TC_TIMING
-  if (tid == 0) atomicAdd(&g_tc_cycles[31], (unsigned long long)(clock64() - tc_kernel_t0));
-#endif
   // ---- teardown ---------------------------------------------------------------------------------
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -829,15 +816,5 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   return BRK_OK;
 }
 
-#ifdef BRK_TC_TIMING
-extern "C" __attribute__((visibility("default"))) int brk_debug_tc_cycles(unsigned long long* out, int reset) {
-  if (cudaMemcpyFromSymbol(out, g_tc_cycles, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
-  if (reset) {
-    unsigned long long z[32] = {};
-    if (cudaMemcpyToSymbol(g_tc_cycles, z, sizeof(z)) != cudaSuccess) return -1;
-  }
-  return 0;
-}
-#endif
 
 }  // namespace brk
