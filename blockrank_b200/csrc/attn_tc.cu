@@ -8,26 +8,28 @@
 // are processed in ping-pong: while one chain's 128 softmax threads work on their S tile, the
 // tensor core runs the other chain's MMAs.
 //
-// Only live key tiles (64 keys) are visited:
+// Only live keys are visited, in 64-key slots (one TMA box each):
 //   block 0            : own keys, causal
 //   document block     : the prefix block's keys, then own keys, causal
 //   query (last) block : every slot of the earlier blocks, then own keys, causal; its context
 //                        is cut into key chunks, each a work item that leaves an un-normalised
 //                        partial (O, max, sum); attn_combine_kernel merges them.
+// Two consecutive slots form one 128-key MMA tile (a document's prefix slot and its first own
+// slot share a tile), which halves the barrier hops per key and runs QK^T at the full N=128 rate.
 //
 // Roles (320 threads):
-//   warps 0-3 / 4-7  softmax + epilogue of chain 0 / 1 (thread = row = TMEM lane)
-//   warp 8           TMA producer: Q tiles and a 4-stage K/V ring, running ahead across items
+//   warps 0-3 / 4-7  softmax + output of chain 0 / 1 (thread = row = TMEM lane)
+//   warp 8           TMA producer: Q tiles and a 2-stage ring of 128-key K/V tiles, running ahead
+//                    across items
 //   warp 9           MMA issuer: S = Q K^T (both operands K-major, 128B swizzle) and O += P V
 //                    (P read from tensor memory, V as the MN-major B operand)
 // O stays in TMEM across the key tiles of an item; softmax is base-2, online, with a lazy
-// rescale (O is only touched when the running max grows by more than 2^8).
+// rescale (O is only touched when the running max grows by more than 2^8).  P (bf16, two keys
+// per 32-bit column) overwrites the first half of the S tile it was computed from.
 //
-// Shared memory 225 KB: Q 2x32 KB, K/V ring 5x32 KB.  TMEM: 2 x (S 2x64 + O 128) columns: S is
-// double buffered per chain so that the next QK^T runs under the current softmax, and P (bf16,
-// two keys per 32-bit column) overwrites the first half of the S buffer it was computed from, so
-// the probabilities never touch shared memory.  No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the
-// thread records a code in the caller's status word, stops waiting and runs to the normal exit.
+// Shared memory 193 KB: Q 2x32 KB, K/V ring 2x64 KB.  TMEM: 2 x (S 128 + O 128) columns.
+// No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the thread records
+// a code in the caller's status word, stops waiting and runs to the normal exit.
 #include <cuda.h>
 
 #include "brk_common.cuh"
@@ -67,22 +69,25 @@ int make_tmap_bf16(CUtensorMap* out, const void* ptr, int D, int heads, int S, i
 }
 
 
+
 namespace {
 
 constexpr int BM = 128;  // query rows (token, head) per row tile
-constexpr int BN = 64;   // keys per tile
+constexpr int BN = 64;   // keys per slot (one TMA box)
+constexpr int BT = 128;  // keys per MMA tile (two slots)
 constexpr int HD = 128;  // head dim
-constexpr int kStages = 5;
+constexpr int kStages = 2;
 constexpr int kThreads = 320;
 constexpr uint32_t kQBytes = 2 * BM * 128;  // two 64-wide halves of D
-constexpr uint32_t kKBytes = 2 * BN * 128;  // one K (or V) tile
+constexpr uint32_t kSlotBytes = 2 * BN * 128;  // K (or V) of one 64-key slot
+constexpr uint32_t kKBytes = 2 * BT * 128;     // one K (or V) tile: [d half][128 keys][128 B]
 constexpr uint32_t kStageBytes = 2 * kKBytes;
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffKV = kOffQ + 2 * kQBytes;
 constexpr uint32_t kOffBar = kOffKV + kStages * kStageBytes;
 constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;  // barriers + slack for the 1024-byte round-up
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kChainCols = 256;  // per chain: S buffers [0,64) and [64,128), then O [128,256)
+constexpr uint32_t kChainCols = 256;  // per chain: S [0,128) (P over its first 64 columns), then O [128,256)
 constexpr uint32_t kColO = 128;
 constexpr float kLazy = 8.f;
 constexpr uint32_t kWaitBudget = 1u << 18;
@@ -90,7 +95,7 @@ constexpr uint32_t kWaitBudget = 1u << 18;
 enum {
   kQFull = 0,    // +chain  TMA -> MMA: Q tile landed
   kQFree = 2,    // +chain  MMA -> TMA: every QK^T of the item has read Q
-  kSFull = 4,    // +2*chain+buffer  MMA -> softmax: S tile complete (S is double buffered per chain)
+  kSFull = 4,    // +chain  MMA -> softmax: S tile complete (+2, +3 unused)
   kPFull = 8,    // +chain  softmax -> MMA: P written to tensor memory, S consumed (4 warp arrivals)
   kPVDone = 10,  // +chain  MMA -> softmax: P V of a tile complete
   kOFree = 12,   // +chain  softmax -> MMA: O read out of TMEM (4 warp arrivals)
@@ -98,6 +103,27 @@ enum {
   kKVFree = 14 + kStages,  // +stage  MMA -> TMA
   kNumBars = 14 + 2 * kStages
 };
+
+// Division by a run-time constant with a host-computed reciprocal (round-up method, exact for every
+// 32-bit numerator): q = umulhi(n, mul); n / d = (((n - q) >> 1) + q) >> shift.
+struct FastDiv {
+  uint32_t d, mul, shift;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d; f.mul = 0; f.shift = 0;
+  if (d <= 1) return f;
+  uint32_t s = 0;
+  while ((1u << s) < d) ++s;  // ceil(log2 d)
+  f.mul = (uint32_t)((((uint64_t)1 << 32) * (((uint64_t)1 << s) - d)) / d + 1);
+  f.shift = s - 1;
+  return f;
+}
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv& f) {
+  if (f.d <= 1) return n;
+  const uint32_t q = __umulhi(n, f.mul);
+  return (((n - q) >> 1) + q) >> f.shift;
+}
 
 struct TcArgs {
   View o;
@@ -113,6 +139,7 @@ struct TcArgs {
   int pairs;        // row-tile pairs per block (covers max_block_len)
   int o_align32;    // output rows are 32-byte aligned (enables 32-byte stores)
   int total_items;
+  FastDiv div_sec1, div_nbg, div_sec2, div_nk;  // by nbg*n_split, nbg, nbg*(M-1), Nk
   float* part_o;    // [B, N, lq_max, n_split, 128] un-normalised partial outputs
   float2* part_ml;  // [B, N, lq_max, n_split] (running max in log2 units, sum)
 };
@@ -148,21 +175,22 @@ __device__ __forceinline__ ItemRaw load_item(const TcArgs& a, int idx) {
   const int sec1 = nbg * a.n_split * a.pairs;
   int bg;
   if (idx < sec1) {
-    r.p = idx / (nbg * a.n_split);
-    const int q = idx % (nbg * a.n_split);
-    r.chunk = q / nbg;
-    bg = q % nbg;
+    r.p = (int)fdiv((uint32_t)idx, a.div_sec1);
+    const int q = idx - r.p * (nbg * a.n_split);
+    r.chunk = (int)fdiv((uint32_t)q, a.div_nbg);
+    bg = q - r.chunk * nbg;
     r.m = a.M - 1;
   } else {
     const int i2 = idx - sec1;
-    r.p = i2 / (nbg * (a.M - 1));
-    const int q = i2 % (nbg * (a.M - 1));
-    r.m = a.M - 2 - q / nbg;
-    bg = q % nbg;
+    r.p = (int)fdiv((uint32_t)i2, a.div_sec2);
+    const int q = i2 - r.p * (nbg * (a.M - 1));
+    const int mm = (int)fdiv((uint32_t)q, a.div_nbg);
+    r.m = a.M - 2 - mm;
+    bg = q - mm * nbg;
     r.chunk = 0;
   }
-  r.b = bg / a.Nk;
-  r.g = bg % a.Nk;
+  r.b = (int)fdiv((uint32_t)bg, a.div_nk);
+  r.g = bg - r.b * a.Nk;
   const int32_t* bs = a.blk_start + (size_t)r.b * a.M;
   const int32_t* bl = a.blk_len + (size_t)r.b * a.M;
   const int m2 = a.M >= 2 ? a.M - 2 : 0;
@@ -331,18 +359,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           ++q_loads[x];
         }
-        for (int j = 0; j < it.n_tiles; ++j) {
-          int nk, own_off; bool own;
-          const int lo = tile_lo(it, j, nk, own, own_off);
+        for (int t = 0; 2 * t < it.n_tiles; ++t) {
           const uint32_t st = kv_cnt % kStages, use = kv_cnt / kStages;
           if (use > 0) wait(kKVFree + st, use - 1, 12);
           const uint32_t dst = sbase + kOffKV + st * kStageBytes;
+          const int nslots = min(2, it.n_tiles - 2 * t);
           if (leader) {
-            ptx::mbar_expect_tx(bar(kKVFull + st), kStageBytes);
-            ptx::tma_load_4d(dst, &tmK, bar(kKVFull + st), 0, it.g, lo, it.b);
-            ptx::tma_load_4d(dst + BN * 128, &tmK, bar(kKVFull + st), 64, it.g, lo, it.b);
-            ptx::tma_load_4d(dst + kKBytes, &tmV, bar(kKVFull + st), 0, it.g, lo, it.b);
-            ptx::tma_load_4d(dst + kKBytes + BN * 128, &tmV, bar(kKVFull + st), 64, it.g, lo, it.b);
+            ptx::mbar_expect_tx(bar(kKVFull + st), (uint32_t)nslots * 2 * kSlotBytes);
+            for (int h = 0; h < nslots; ++h) {
+              int nk, own_off; bool own;
+              const int lo = tile_lo(it, 2 * t + h, nk, own, own_off);
+              const uint32_t row = dst + (uint32_t)h * (BN * 128);  // slot h = key rows [64h, 64h+64) of the tile
+              ptx::tma_load_4d(row, &tmK, bar(kKVFull + st), 0, it.g, lo, it.b);
+              ptx::tma_load_4d(row + BT * 128, &tmK, bar(kKVFull + st), 64, it.g, lo, it.b);
+              ptx::tma_load_4d(row + kKBytes, &tmV, bar(kKVFull + st), 0, it.g, lo, it.b);
+              ptx::tma_load_4d(row + kKBytes + BT * 128, &tmV, bar(kKVFull + st), 64, it.g, lo, it.b);
+            }
           }
           ++kv_cnt;
         }
@@ -354,46 +386,48 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // MMAs of the thread that executes it).
     {
       const bool leader = lane == 0;
-      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0}, s_cnt[2] = {0, 0},
-               pv_cnt[2] = {0, 0};
+      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0};
       // Descriptors are built once: every operand buffer has a fixed address, and stepping along K
       // or to another ring stage only adds a constant to the 16-byte-unit start-address field.
       const uint32_t idesc_pv = ptx::idesc_bf16(BM, HD, 0, 1);
       const uint32_t idesc_qk0 = ptx::idesc_bf16(BM, 0, 0, 0);
       const uint64_t q_desc0 = ptx::smem_desc_sw128(sbase + kOffQ, 16, 1024);
       const uint64_t k_desc0 = ptx::smem_desc_sw128(sbase + kOffKV, 16, 1024);
-      const uint64_t v_desc0 = ptx::smem_desc_sw128(sbase + kOffKV + kKBytes, BN * 128, 1024);
-      auto issue_qk = [&](int x, int nk, bool last, uint32_t st) {
-        const uint32_t idesc = idesc_qk0 | ((uint32_t)((nk + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
+      const uint64_t v_desc0 = ptx::smem_desc_sw128(sbase + kOffKV + kKBytes, BT * 128, 1024);
+      // keys of tile t that chain x (seeing n_vis slots) multiplies: full first slot + the valid part of the last one
+      auto tile_keys = [&](const Item& it, int t, int n_vis) {
+        const int cnt = min(2, n_vis - 2 * t);
+        int nk, own_off; bool own;
+        tile_lo(it, 2 * t + cnt - 1, nk, own, own_off);
+        return (cnt - 1) * BN + nk;
+      };
+      auto issue_qk = [&](int x, int keys, bool last, uint32_t st) {
+        const uint32_t idesc = idesc_qk0 | ((uint32_t)((keys + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
         const uint64_t ad = q_desc0 + (uint64_t)((uint32_t)x * (kQBytes >> 4));
         const uint64_t bd = k_desc0 + (uint64_t)(st * (kStageBytes >> 4));
-        const uint32_t buf = s_cnt[x] & 1u;
-        const uint32_t d = tmem + (uint32_t)x * kChainCols + buf * BN;
+        const uint32_t d = tmem + (uint32_t)x * kChainCols;
         if (leader) {
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks) {
             const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
-            const uint32_t boff = (uint32_t)(ks >> 2) * ((BN * 128) >> 4) + (uint32_t)(ks & 3) * 2;
+            const uint32_t boff = (uint32_t)(ks >> 2) * ((BT * 128) >> 4) + (uint32_t)(ks & 3) * 2;
             ptx::mma_ss(d, ad + aoff, bd + boff, idesc, ks > 0);
           }
-          ptx::mma_commit(bar(kSFull + 2 * x + (int)buf));
+          ptx::mma_commit(bar(kSFull + x));
           if (last) ptx::mma_commit(bar(kQFree + x));  // last read of this chain's Q tile
         }
-        ++s_cnt[x];
       };
-      auto issue_pv = [&](int x, int nk, bool first, uint32_t st) {
-        // P of this tile sits in the S buffer the tile was computed in (tiles alternate buffers)
-        const uint32_t pa = tmem + (uint32_t)x * kChainCols + (pv_cnt[x] & 1u) * BN;
+      auto issue_pv = [&](int x, int keys, bool first, uint32_t st) {
+        const uint32_t pa = tmem + (uint32_t)x * kChainCols;  // P sits over the first 64 columns of S
         const uint64_t bd = v_desc0 + (uint64_t)(st * (kStageBytes >> 4));
         const uint32_t d = tmem + (uint32_t)x * kChainCols + kColO;
-        const int ksteps = (nk + 15) >> 4;
+        const int ksteps = (keys + 15) >> 4;
         if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < BN / 16; ++ks)
+          for (int ks = 0; ks < BT / 16; ++ks)
             if (ks < ksteps) ptx::mma_ts(d, pa + (uint32_t)ks * 8, bd + (uint32_t)ks * ((16 * 128) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
           ptx::mma_commit(bar(kPVDone + x));
         }
-        ++pv_cnt[x];
       };
       ItemRaw raw_next = load_item(a, blockIdx.x);
       for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
@@ -402,148 +436,56 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const Item it = decode_item(a, raw);
         if (!it.valid) continue;
         const int n0 = it.n_0, n1 = it.n_1;
+        const int T0 = (n0 + 1) >> 1, T1 = (n1 + 1) >> 1, T = (it.n_tiles + 1) >> 1;
 #pragma unroll
         for (int x = 0; x < 2; ++x)
           if ((x == 0 ? n0 : n1) > 0) { wait(kQFull + x, q_uses[x], 20 + x); ++q_uses[x]; }
         int kv_waited = -1;
-        auto need_kv = [&](int j) {
-          if (kv_waited >= j) return;
-          const uint32_t gidx = kv_cnt + (uint32_t)j;
+        auto need_kv = [&](int t) {
+          if (kv_waited >= t) return;
+          const uint32_t gidx = kv_cnt + (uint32_t)t;
           wait(kKVFull + gidx % kStages, gidx / kStages, 22);
-          kv_waited = j;
-        };
-        auto tile_nk = [&](int j) {
-          int nk, own_off; bool own;
-          tile_lo(it, j, nk, own, own_off);
-          return nk;
+          kv_waited = t;
         };
         need_kv(0);
         ptx::tc_fence_after_sync();
-        {
-          const int nk = tile_nk(0);
 #pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            const int nx = x == 0 ? n0 : n1;
-            if (nx > 0) issue_qk(x, nk, nx == 1, kv_cnt % kStages);
-          }
+        for (int x = 0; x < 2; ++x) {
+          const int nx = x == 0 ? n0 : n1, Tx = x == 0 ? T0 : T1;
+          if (Tx > 0) issue_qk(x, tile_keys(it, 0, nx), Tx == 1, kv_cnt % kStages);
         }
-        int nk_cur = tile_nk(0);
-        for (int j = 0; j < it.n_tiles; ++j) {
-          const uint32_t st = (kv_cnt + (uint32_t)j) % kStages;
-          const int nk_next = (j + 1 < it.n_tiles) ? tile_nk(j + 1) : 0;
-          // next tile's QK^T first: it lands in the chain's other S buffer (whose last reader, the
-          // softmax of tile j-1, has already signalled) and runs under the softmax of tile j
+        for (int t = 0; t < T; ++t) {
+          const uint32_t st = (kv_cnt + (uint32_t)t) % kStages;
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            const int nx = x == 0 ? n0 : n1;
-            if (j + 1 < nx) {
-              need_kv(j + 1);
-              ptx::tc_fence_after_sync();
-              issue_qk(x, nk_next, j + 2 == nx, (kv_cnt + (uint32_t)j + 1) % kStages);
-            }
-          }
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            const int nx = x == 0 ? n0 : n1;
-            if (j >= nx) continue;
+            const int nx = x == 0 ? n0 : n1, Tx = x == 0 ? T0 : T1;
+            if (t >= Tx) continue;
             wait(kPFull + x, p_seen[x], 24 + x);
             ++p_seen[x];
-            if (j == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
+            if (t == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
             ptx::tc_fence_after_sync();
-            issue_pv(x, nk_cur, j == 0, st);
+            issue_pv(x, tile_keys(it, t, nx), t == 0, st);
+            if (t + 1 < Tx) {
+              // the chain's next S tile: queued behind the P V that reads P out of the same columns
+              need_kv(t + 1);
+              ptx::tc_fence_after_sync();
+              issue_qk(x, tile_keys(it, t + 1, nx), t + 2 == Tx, (kv_cnt + (uint32_t)t + 1) % kStages);
+            }
           }
           if (leader) ptx::mma_commit(bar(kKVFree + st));  // both chains' MMAs on this stage are queued
-          nk_cur = nk_next;
         }
-        kv_cnt += (uint32_t)it.n_tiles;
+        kv_cnt += (uint32_t)T;
 #pragma unroll
         for (int x = 0; x < 2; ++x)
           if ((x == 0 ? n0 : n1) > 0) ++items_done[x];
       }
     }
   } else {
-    // =============================== softmax + epilogue, chain x ================================
+    // =============================== softmax + output, chain x ==================================
     const int x = warp >> 2;
     const int r = tid & 127;  // row of the tile = TMEM lane
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)x * kChainCols;
     uint32_t s_seen = 0, pv_seen = 0;
-
-    // What the drain of an item's output needs once its last key tile has been handed to the MMA.
-    // (Draining one tile late, behind the next item's first softmax tile, was measured slower.)
-    struct Pending {
-      bool any, split, write;
-      __nv_bfloat16* out_row;  // normal item: this thread's output row
-      float* lse_ptr;          // normal item: where the row's log-sum-exp goes (or null)
-      int64_t prow;            // split item: row of the partial buffers
-      float m_run, l_run;
-    } pend;
-    pend.any = false;
-
-    auto drain = [&]() {
-      wait(kPVDone + x, pv_seen, 34 + x);  // last P V of that item
-      ++pv_seen;
-      ptx::tc_fence_after_sync();
-      __syncwarp();
-      if (pend.split) {
-        // un-normalised partial (O, max, sum) of a key chunk; merged by attn_combine_kernel
-#pragma unroll 1
-        for (int ch = 0; ch < HD / 32; ++ch) {
-          uint32_t orow[32];
-          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-          ptx::tmem_wait_ld();
-          if (pend.write) {
-            float4* dst = reinterpret_cast<float4*>(a.part_o + pend.prow * HD + ch * 32);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              dst[i] = make_float4(__uint_as_float(orow[4 * i]), __uint_as_float(orow[4 * i + 1]),
-                                   __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
-          }
-        }
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
-        if (pend.write) a.part_ml[pend.prow] = make_float2(pend.m_run, pend.l_run);
-      } else {
-        // O / l -> bf16, stored straight from registers: each thread owns one 256-byte output row
-        // and writes it as eight 32-byte (full-sector) stores, or sixteen 16-byte ones if the
-        // output is only 16-byte aligned.
-        const float inv = pend.l_run > 0.f ? 1.f / pend.l_run : 0.f;
-        auto store32 = [&](const uint32_t (&orow)[32], int ch) {
-#pragma unroll
-          for (int q8 = 0; q8 < 2; ++q8) {
-            uint32_t w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(orow[q8 * 16 + 2 * i]) * inv,
-                                                        __uint_as_float(orow[q8 * 16 + 2 * i + 1]) * inv);
-              w[i] = *reinterpret_cast<uint32_t*>(&hh);
-            }
-            __nv_bfloat16* dst = pend.out_row + ch * 32 + q8 * 16;
-            if (a.o_align32) {
-              ptx::st_global_v8(dst, w);
-            } else {
-              *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-            }
-          }
-        };
-#pragma unroll 1
-        for (int ch = 0; ch < HD / 32; ++ch) {
-          uint32_t orow[32];
-          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-          ptx::tmem_wait_ld();
-          if (ch == HD / 32 - 1) {  // O is out of TMEM: the next item's first P V may overwrite it
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
-          }
-          if (pend.write) store32(orow, ch);
-        }
-        if (pend.write && pend.lse_ptr != nullptr)
-          *pend.lse_ptr = (pend.m_run + log2f(pend.l_run)) * 0.6931471805599453f;
-      }
-      pend.any = false;
-    };
 
     ItemRaw raw_next = load_item(a, blockIdx.x);
     for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
@@ -566,33 +508,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       float m_run = -INFINITY, l_run = 0.f;
       const int n_mine = it.n_x(x);
-      for (int j = 0; j < n_mine; ++j) {
+      const int t_mine = (n_mine + 1) >> 1;
+
+      // 64 logits of one slot: TMEM -> registers, invisible keys set to -inf
+      auto load_slot = [&](int slot, int h, uint32_t (&sr)[64]) {
         int nk, own_off; bool own;
-        const int lo = tile_lo(it, j, nk, own, own_off);
-        const uint32_t buf = s_seen & 1u;
-        wait(kSFull + 2 * x + (int)buf, s_seen >> 1, 30 + x);
-        ++s_seen;
-        ptx::tc_fence_after_sync();
-        __syncwarp();
-        uint32_t sr[64];
+        const int lo = tile_lo(it, slot, nk, own, own_off);
         {
           uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
           uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
-          {
-          ptx::tmem_ld32(tmem_lane + buf * BN, lo32);
-          ptx::tmem_ld32(tmem_lane + buf * BN + 32, hi32);
+          ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN, lo32);
+          ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN + 32, hi32);
           ptx::tmem_wait_ld();
-          }
         }
-        // Tiles fully inside the visible region need no per-element masking (the common case);
+        // Slots fully inside the visible region need no per-element masking (the common case);
         // ragged tails, the causal diagonal and padded context ranges take the masked path.
         const bool need_mask = nk < BN || (own && own_off + BN - 1 > it.t0(x)) || (!own && ctx_check);
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
-        if (!need_mask) {
-#pragma unroll
-          for (int c = 0; c < 64; c += 2)
-            mx4[(c >> 1) & 3] = ptx::max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-        } else {
+        if (need_mask) {
           int lim = nk;  // columns [0, lim) are visible to this row
           if (own) lim = max(0, min(nk, tok - own_off + 1));
           unsigned v0 = 0xffffffffu, v1 = 0xffffffffu;
@@ -603,10 +535,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
           for (int c = 0; c < 64; ++c) {
             const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
-            const float sv = ok ? __uint_as_float(sr[c]) : -INFINITY;
-            sr[c] = __float_as_uint(sv);
-            mx4[c & 3] = fmaxf(mx4[c & 3], sv);
+            sr[c] = ok ? sr[c] : 0xff800000u;  // -inf
           }
+        }
+      };
+
+      for (int t = 0; t < t_mine; ++t) {
+        const int cnt = min(2, n_mine - 2 * t);  // slots of this tile the chain sees
+        wait(kSFull + x, s_seen, 30 + x);
+        ++s_seen;
+        ptx::tc_fence_after_sync();
+        __syncwarp();
+        // pass 1: row maximum over the tile
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+        for (int h = 0; h < cnt; ++h) {
+          uint32_t sr[64];
+          load_slot(2 * t + h, h, sr);
+#pragma unroll
+          for (int c = 0; c < 64; c += 2)
+            mx4[(c >> 1) & 3] = ptx::max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
         float m_new = fmaxf(m_run, mx);
@@ -614,36 +561,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
         const float corr = ptx::ex2(m_run - m_ref);  // 1 when unchanged, 0 on the first visible tile
         const float neg_ref = -m_ref;
-        // p = 2^(s*scale - m) with packed fp32x2 arithmetic.  Every second pair of exponentials is
-        // evaluated on the FMA pipe: the special-function unit (16 results per clock per SM) would
-        // otherwise bound the whole kernel.
-        const ptx::f32x2 sc2 = ptx::pack2(a.scale_log2, a.scale_log2), nr2 = ptx::pack2(neg_ref, neg_ref);
-        ptx::f32x2 ps2[2] = {0ull, 0ull};
-        uint32_t pk[32];
-#pragma unroll
-        for (int c = 0; c < 64; c += 4) {
-          const ptx::f32x2 t01 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nr2);
-          const ptx::f32x2 t23 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nr2);
-          float t0, t1, p2, p3;
-          ptx::unpack2(t01, t0, t1);
-          const float p0 = ptx::ex2(t0), p1 = ptx::ex2(t1);
-          const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
-          ptx::unpack2(p23, p2, p3);
-          ps2[0] = ptx::add2(ps2[0], ptx::pack2(p0, p1));
-          ps2[1] = ptx::add2(ps2[1], p23);
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
-          pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
-          pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
-        }
-        float s0, s1, s2, s3;
-        ptx::unpack2(ps2[0], s0, s1);
-        ptx::unpack2(ps2[1], s2, s3);
-        l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
         const bool changed = m_new != m_run;
         m_run = m_new;
 
-        if (j > 0) {
-          wait(kPVDone + x, pv_seen, 32 + x);  // previous P V done: O is stable
+        if (t > 0) {
+          // previous P V done: O is stable and the P columns (first half of S) may be overwritten
+          wait(kPVDone + x, pv_seen, 32 + x);
           ++pv_seen;
           ptx::tc_fence_after_sync();
           if (__any_sync(0xffffffffu, changed)) {
@@ -659,32 +582,109 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ptx::tmem_wait_st();
           }
         }
-        // P row -> tensor memory, over the first 32 columns of the S buffer it came from
-        {
-        ptx::tmem_st32(tmem_lane + buf * BN, pk);
-        ptx::tmem_wait_st();
+        // pass 2: p = 2^(s*scale - m) with packed fp32x2 arithmetic, slot by slot; P of slot h goes to
+        // columns [32h, 32h+32), which only covers logits that have already been consumed.  Every
+        // second pair of exponentials is evaluated on the FMA pipe: the special-function unit
+        // (16 results per clock per SM) would otherwise bound the whole kernel.
+        const ptx::f32x2 sc2 = ptx::pack2(a.scale_log2, a.scale_log2), nr2 = ptx::pack2(neg_ref, neg_ref);
+        ptx::f32x2 ps2[2] = {0ull, 0ull};
+        for (int h = 0; h < cnt; ++h) {
+          uint32_t sr[64];
+          load_slot(2 * t + h, h, sr);
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 64; c += 4) {
+            const ptx::f32x2 t01 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nr2);
+            const ptx::f32x2 t23 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nr2);
+            float t0, t1, p2, p3;
+            ptx::unpack2(t01, t0, t1);
+            const float p0 = ptx::ex2(t0), p1 = ptx::ex2(t1);
+            const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
+            ptx::unpack2(p23, p2, p3);
+            ps2[0] = ptx::add2(ps2[0], ptx::pack2(p0, p1));
+            ps2[1] = ptx::add2(ps2[1], p23);
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+            pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+            pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
+          }
+          ptx::tmem_st32(tmem_lane + (uint32_t)h * 32, pk);
         }
+        float s0, s1, s2, s3;
+        ptx::unpack2(ps2[0], s0, s1);
+        ptx::unpack2(ps2[1], s2, s3);
+        l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
+        ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar(kPFull + x));
       }
-      pend.any = true;
-      pend.split = it.split;
-      pend.m_run = m_run;
-      pend.l_run = l_run;
+
+      // ---- output of the item ----
+      wait(kPVDone + x, pv_seen, 34 + x);  // last P V of the item
+      ++pv_seen;
+      ptx::tc_fence_after_sync();
+      __syncwarp();
       if (it.split) {
-        pend.write = active && tok < a.lq_max;
-        pend.prow = (((int64_t)it.b * a.N + n) * a.lq_max + tok) * a.n_split + it.chunk;
-        pend.out_row = nullptr;
-        pend.lse_ptr = nullptr;
+        // un-normalised partial (O, max, sum) of this key chunk; merged by attn_combine_kernel
+        const bool wr = active && tok < a.lq_max;
+        const int64_t prow = (((int64_t)it.b * a.N + n) * a.lq_max + tok) * a.n_split + it.chunk;
+#pragma unroll 1
+        for (int ch = 0; ch < HD / 32; ++ch) {
+          uint32_t orow[32];
+          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+          ptx::tmem_wait_ld();
+          if (wr) {
+            float4* dst = reinterpret_cast<float4*>(a.part_o + prow * HD + ch * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(orow[4 * i]), __uint_as_float(orow[4 * i + 1]),
+                                   __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
+        if (wr) a.part_ml[prow] = make_float2(m_run, l_run);
       } else {
-        pend.write = active;
-        pend.prow = 0;
-        pend.out_row = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb +
-                       (int64_t)(it.start + tok) * a.o.ss + (int64_t)n * a.o.sh;
-        pend.lse_ptr = a.lse != nullptr ? a.lse + ((int64_t)it.b * a.N + n) * a.S + it.start + tok : nullptr;
+        // O / l -> bf16, stored straight from registers: each thread owns one 256-byte output row
+        // and writes it as eight 32-byte (full-sector) stores, or sixteen 16-byte ones if the
+        // output is only 16-byte aligned.
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb +
+                                 (int64_t)(it.start + tok) * a.o.ss + (int64_t)n * a.o.sh;
+#pragma unroll 1
+        for (int ch = 0; ch < HD / 32; ++ch) {
+          uint32_t orow[32];
+          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+          ptx::tmem_wait_ld();
+          if (ch == HD / 32 - 1) {  // O is out of TMEM: the next item's first P V may overwrite it
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
+          }
+          if (active) {
+#pragma unroll
+            for (int q8 = 0; q8 < 2; ++q8) {
+              uint32_t w[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(orow[q8 * 16 + 2 * i]) * inv,
+                                                          __uint_as_float(orow[q8 * 16 + 2 * i + 1]) * inv);
+                w[i] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              __nv_bfloat16* dst = out_row + ch * 32 + q8 * 16;
+              if (a.o_align32) {
+                ptx::st_global_v8(dst, w);
+              } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+              }
+            }
+          }
+        }
+        if (active && a.lse != nullptr)
+          a.lse[((int64_t)it.b * a.N + n) * a.S + it.start + tok] = (m_run + log2f(l_run)) * 0.6931471805599453f;
       }
-      drain();
     }
   }
 
@@ -798,6 +798,10 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   a.pairs = pairs;
   a.o_align32 = (((uintptr_t)p.o.ptr & 31) == 0 && p.o.stride_b % 16 == 0 && p.o.stride_h % 16 == 0 && p.o.stride_s % 16 == 0) ? 1 : 0;
   a.total_items = (int)total_items;
+  a.div_sec1 = make_fastdiv((uint32_t)(p.B * p.Nk * ns));
+  a.div_nbg = make_fastdiv((uint32_t)(p.B * p.Nk));
+  a.div_sec2 = make_fastdiv((uint32_t)(p.B * p.Nk * (p.M > 1 ? p.M - 1 : 1)));
+  a.div_nk = make_fastdiv((uint32_t)p.Nk);
   const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
   a.part_o = ns > 1 ? reinterpret_cast<float*>(ws) : nullptr;
   a.part_ml = ns > 1 ? reinterpret_cast<float2*>(reinterpret_cast<float*>(ws) + rows * HD) : nullptr;
@@ -815,6 +819,7 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   }
   return BRK_OK;
 }
+
 
 
 }  // namespace brk
