@@ -519,7 +519,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
           ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN, lo32);
           ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN + 32, hi32);
-          ptx::tmem_wait_ld();
+          ptx::tmem_wait_ld(sr);
         }
         // Slots fully inside the visible region need no per-element masking (the common case);
         // ragged tails, the causal diagonal and padded context ranges take the masked path.
@@ -574,7 +574,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int ch = 0; ch < HD / 32; ++ch) {
               uint32_t orow[32];
               ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-              ptx::tmem_wait_ld();
+              ptx::tmem_wait_ld(orow);
 #pragma unroll
               for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
               ptx::tmem_st32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
@@ -632,7 +632,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int ch = 0; ch < HD / 32; ++ch) {
           uint32_t orow[32];
           ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-          ptx::tmem_wait_ld();
+          ptx::tmem_wait_ld(orow);
           if (wr) {
             float4* dst = reinterpret_cast<float4*>(a.part_o + prow * HD + ch * 32);
 #pragma unroll
@@ -656,7 +656,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int ch = 0; ch < HD / 32; ++ch) {
           uint32_t orow[32];
           ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-          ptx::tmem_wait_ld();
+          ptx::tmem_wait_ld(orow);
           if (ch == HD / 32 - 1) {  // O is out of TMEM: the next item's first P V may overwrite it
             ptx::tc_fence_before_sync();
             __syncwarp();

@@ -46,6 +46,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   return false;
 }
 
+// Non-blocking test of a phase parity.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // 2^x on the special-function unit (flush-to-zero; 2^-inf = +0)
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -214,6 +227,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Wait for outstanding tcgen05.ld, then tie the destination registers to the wait: the loaded
+// values are only defined after wait::ld, but to the compiler the wait has no data dependence on
+// them, so arithmetic on the registers could legally be scheduled above it.  Passing every
+// register through an empty volatile asm (kept in program order with the wait) closes that hole
+// at no instruction cost.
+template <int N>
+__device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[N]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i])::"memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 }  // namespace ptx
