@@ -32,6 +32,8 @@
 // a code in the caller's status word, stops waiting and runs to the normal exit.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "brk_common.cuh"
 #include "tc_ptx.cuh"
 
@@ -85,7 +87,9 @@ constexpr uint32_t kStageBytes = 2 * kKBytes;
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffKV = kOffQ + 2 * kQBytes;
 constexpr uint32_t kOffBar = kOffKV + kStages * kStageBytes;
-constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;  // barriers + slack for the 1024-byte round-up
+constexpr int kItemRing = 4;                        // decoded work items in flight between the producer and its consumers
+constexpr uint32_t kOffItems = kOffBar + 256;       // kItemRing records of 16 ints
+constexpr uint32_t kSmemBytes = kOffItems + kItemRing * 64 + 1024;  // + slack for the 1024-byte round-up
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kChainCols = 256;  // per chain: S [0,128) (P over its first 64 columns), then O [128,256)
 constexpr uint32_t kColO = 128;
@@ -101,8 +105,11 @@ enum {
   kOFree = 12,   // +chain  softmax -> MMA: O read out of TMEM (4 warp arrivals)
   kKVFull = 14,  // +stage  TMA -> MMA
   kKVFree = 14 + kStages,  // +stage  MMA -> TMA
-  kNumBars = 14 + 2 * kStages
+  kItemFull = 14 + 2 * kStages,           // +ring slot  TMA warp -> MMA, softmax: item record written
+  kItemFree = kItemFull + kItemRing,      // +ring slot  MMA + 8 softmax warps -> TMA warp: record copied (9 arrivals)
+  kNumBars = kItemFree + kItemRing
 };
+static_assert(kNumBars * 8 + 4 <= 256, "barrier area");
 
 // Division by a run-time constant with a host-computed reciprocal (round-up method, exact for every
 // 32-bit numerator): q = umulhi(n, mul); n / d = (((n - q) >> 1) + q) >> shift.
@@ -264,6 +271,31 @@ __device__ __forceinline__ int tile_lo(const Item& it, int j, int& nk, bool& own
   return it.start + own_off;
 }
 
+// Work items are decoded once, by the TMA warp, and handed to the MMA warp and the softmax warps as
+// 16-int records in shared memory: decoding costs two global-memory round trips and a few hundred
+// scalar instructions, which would otherwise sit on every role's critical path between two items.
+constexpr int kRecSplit = 1, kRecCtxCheck = 2, kRecStop = 4;
+__device__ __forceinline__ void write_record(int* rec, const Item& it, int flags) {
+  reinterpret_cast<int4*>(rec)[0] = make_int4(it.b, it.g, it.m, it.chunk);
+  reinterpret_cast<int4*>(rec)[1] = make_int4(it.start, it.len, it.t0_0, it.n_0);
+  reinterpret_cast<int4*>(rec)[2] = make_int4(it.n_1, it.ctx_lo, it.ctx_hi, it.n_ctx);
+  reinterpret_cast<int4*>(rec)[3] = make_int4(it.j0, it.n_tiles, it.own_n, flags);
+}
+__device__ __forceinline__ Item read_record(const int* rec, int tok_per_tile, int& flags) {
+  const int4 r0 = reinterpret_cast<const int4*>(rec)[0], r1 = reinterpret_cast<const int4*>(rec)[1];
+  const int4 r2 = reinterpret_cast<const int4*>(rec)[2], r3 = reinterpret_cast<const int4*>(rec)[3];
+  Item it;
+  it.b = r0.x; it.g = r0.y; it.m = r0.z; it.chunk = r0.w;
+  it.start = r1.x; it.len = r1.y; it.t0_0 = r1.z; it.n_0 = r1.w;
+  it.t0_1 = it.t0_0 + tok_per_tile;
+  it.n_1 = r2.x; it.ctx_lo = r2.y; it.ctx_hi = r2.z; it.n_ctx = r2.w;
+  it.j0 = r3.x; it.n_tiles = r3.y; it.own_n = r3.z;
+  flags = r3.w;
+  it.split = (flags & kRecSplit) != 0;
+  it.valid = true;
+  return it;
+}
+
 // slot -> is it inside some block?  (blk_start is non-decreasing)
 __device__ __forceinline__ bool slot_valid(const int32_t* bs, const int32_t* bl, int M, int s) {
   int lo = 0, hi = M;
@@ -310,7 +342,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (tid == 0) {
     for (int i = 0; i < kNumBars; ++i) {
       const bool many = (i >= kPFull && i < kPFull + 2) || (i >= kOFree && i < kOFree + 2);
-      ptx::mbar_init(bar(i), many ? 4u : 1u);  // one arrival per softmax warp
+      const bool rec_free = i >= kItemFree && i < kItemFree + kItemRing;
+      ptx::mbar_init(bar(i), rec_free ? 9u : many ? 4u : 1u);  // one arrival per softmax warp (+ the MMA warp)
     }
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmQ);
@@ -335,19 +368,53 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   };
 
+  int* const item_ring = reinterpret_cast<int*>(smem + kOffItems);
+  const int TOK = BM >> a.g_shift;
+  // consumer side of the item ring: copy record number i, release its slot
+  auto next_item = [&](uint32_t i, int& flags) {
+    const uint32_t slot = i % kItemRing;
+    wait(kItemFull + slot, i / kItemRing, 40);
+    Item it = read_record(item_ring + slot * 16, TOK, flags);
+    if (__any_sync(0xffffffffu, failed)) flags |= kRecStop;  // a wait gave up: the whole warp stops here
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(bar(kItemFree + slot));
+    return it;
+  };
+
   if (warp == 8) {
     // =============================== TMA producer ===============================================
     // The whole warp runs the control flow (so addresses and counters stay warp-uniform); one lane
     // issues the copies.
     {
       const bool leader = lane == 0;
-      uint32_t kv_cnt = 0, q_loads[2] = {0, 0};
+      uint32_t kv_cnt = 0, q_loads[2] = {0, 0}, n_pub = 0;
+      // record number n_pub -> ring; its slot must have been copied by all nine consumers
+      auto publish = [&](const Item& it, int flags) {
+        const uint32_t slot = n_pub % kItemRing;
+        if (n_pub >= kItemRing) wait(kItemFree + slot, n_pub / kItemRing - 1, 14);
+        if (leader) {
+          write_record(item_ring + slot * 16, it, flags);
+          ptx::mbar_arrive(bar(kItemFull + slot));  // release: the record is visible to whoever sees the phase flip
+        }
+        ++n_pub;
+      };
       ItemRaw raw_next = load_item(a, blockIdx.x);
+      Item it{};
       for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
         const ItemRaw raw = raw_next;
         raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
-        const Item it = decode_item(a, raw);
+        it = decode_item(a, raw);
         if (!it.valid) continue;
+        int flags = it.split ? kRecSplit : 0;
+        if (it.m == a.M - 1 && it.m > 0) {  // the query block's context may contain padding slots
+          const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
+          int part = 0;
+          for (int i = lane; i < a.M - 1; i += 32) part += bl[i];
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+          if (part != (it.ctx_hi - it.ctx_lo)) flags |= kRecCtxCheck;
+        }
+        publish(it, flags);
         for (int x = 0; x < 2; ++x) {
           if (it.n_x(x) == 0) continue;
           if (q_loads[x] > 0) wait(kQFree + x, q_loads[x] - 1, 10 + x);
@@ -379,6 +446,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           ++kv_cnt;
         }
       }
+      publish(it, kRecStop);  // end of this CTA's work list
     }
   } else if (warp == 9) {
     // =============================== MMA issuer =================================================
@@ -429,12 +497,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           ptx::mma_commit(bar(kPVDone + x));
         }
       };
-      ItemRaw raw_next = load_item(a, blockIdx.x);
-      for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
-        const ItemRaw raw = raw_next;
-        raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
-        const Item it = decode_item(a, raw);
-        if (!it.valid) continue;
+      for (uint32_t item_no = 0;; ++item_no) {
+        int flags;
+        const Item it = next_item(item_no, flags);
+        if (flags & kRecStop) break;
         const int n0 = it.n_0, n1 = it.n_1;
         const int T0 = (n0 + 1) >> 1, T1 = (n1 + 1) >> 1, T = (it.n_tiles + 1) >> 1;
 #pragma unroll
@@ -487,58 +553,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)x * kChainCols;
     uint32_t s_seen = 0, pv_seen = 0;
 
-    ItemRaw raw_next = load_item(a, blockIdx.x);
-    for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
-      const ItemRaw raw = raw_next;
-      raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
-      const Item it = decode_item(a, raw);
-      if (!it.valid || it.n_x(x) == 0) continue;
+    for (uint32_t item_no = 0;; ++item_no) {
+      int flags;
+      const Item it = next_item(item_no, flags);
+      if (flags & kRecStop) break;
+      if (it.n_x(x) == 0) continue;
       const int32_t* bs = a.blk_start + (size_t)it.b * a.M;
       const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
       const int tok = it.t0(x) + (r >> a.g_shift);
       const int n = it.g * G + (r & (G - 1));
       const bool active = tok < it.len;
-      bool ctx_check = false;  // the query block's context may contain padding slots
-      if (it.m == a.M - 1 && it.m > 0) {
-        int part = 0;
-        for (int i = lane; i < a.M - 1; i += 32) part += bl[i];
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-        ctx_check = part != (it.ctx_hi - it.ctx_lo);
-      }
+      const bool ctx_check = (flags & kRecCtxCheck) != 0;  // the query block's context contains padding slots
       float m_run = -INFINITY, l_run = 0.f;
       const int n_mine = it.n_x(x);
       const int t_mine = (n_mine + 1) >> 1;
-
-      // 64 logits of one slot: TMEM -> registers, invisible keys set to -inf
-      auto load_slot = [&](int slot, int h, uint32_t (&sr)[64]) {
-        int nk, own_off; bool own;
-        const int lo = tile_lo(it, slot, nk, own, own_off);
-        {
-          uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
-          uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
-          ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN, lo32);
-          ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN + 32, hi32);
-          ptx::tmem_wait_ld(sr);
-        }
-        // Slots fully inside the visible region need no per-element masking (the common case);
-        // ragged tails, the causal diagonal and padded context ranges take the masked path.
-        const bool need_mask = nk < BN || (own && own_off + BN - 1 > it.t0(x)) || (!own && ctx_check);
-        if (need_mask) {
-          int lim = nk;  // columns [0, lim) are visible to this row
-          if (own) lim = max(0, min(nk, tok - own_off + 1));
-          unsigned v0 = 0xffffffffu, v1 = 0xffffffffu;
-          if (!own && ctx_check) {
-            v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
-            v1 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + 32 + lane));
-          }
-#pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
-            sr[c] = ok ? sr[c] : 0xff800000u;  // -inf
-          }
-        }
-      };
 
       for (int t = 0; t < t_mine; ++t) {
         const int cnt = min(2, n_mine - 2 * t);  // slots of this tile the chain sees
@@ -546,73 +574,142 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ++s_seen;
         ptx::tc_fence_after_sync();
         __syncwarp();
-        // pass 1: row maximum over the tile
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
-        for (int h = 0; h < cnt; ++h) {
-          uint32_t sr[64];
-          load_slot(2 * t + h, h, sr);
-#pragma unroll
-          for (int c = 0; c < 64; c += 2)
-            mx4[(c >> 1) & 3] = ptx::max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
-        float m_new = fmaxf(m_run, mx);
-        if (m_run != -INFINITY && m_new - m_run <= kLazy) m_new = m_run;  // keep the old reference: p <= 2^8
-        const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-        const float corr = ptx::ex2(m_run - m_ref);  // 1 when unchanged, 0 on the first visible tile
-        const float neg_ref = -m_ref;
-        const bool changed = m_new != m_run;
-        m_run = m_new;
-
-        if (t > 0) {
-          // previous P V done: O is stable and the P columns (first half of S) may be overwritten
-          wait(kPVDone + x, pv_seen, 32 + x);
-          ++pv_seen;
-          ptx::tc_fence_after_sync();
-          if (__any_sync(0xffffffffu, changed)) {
+        // One pass per 64-key slot: logits -> registers, mask, row maximum, running-max update,
+        // p = 2^(s*scale - m) from the same registers, P (bf16) -> columns [32h, 32h+32) of the
+        // tile, which only covers logits that have already been consumed.
 #pragma unroll 1
-            for (int ch = 0; ch < HD / 32; ++ch) {
-              uint32_t orow[32];
-              ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-              ptx::tmem_wait_ld(orow);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
-              ptx::tmem_st32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-            }
-            ptx::tmem_wait_st();
-          }
-        }
-        // pass 2: p = 2^(s*scale - m) with packed fp32x2 arithmetic, slot by slot; P of slot h goes to
-        // columns [32h, 32h+32), which only covers logits that have already been consumed.  Every
-        // second pair of exponentials is evaluated on the FMA pipe: the special-function unit
-        // (16 results per clock per SM) would otherwise bound the whole kernel.
-        const ptx::f32x2 sc2 = ptx::pack2(a.scale_log2, a.scale_log2), nr2 = ptx::pack2(neg_ref, neg_ref);
-        ptx::f32x2 ps2[2] = {0ull, 0ull};
         for (int h = 0; h < cnt; ++h) {
+          int nk, own_off; bool own;
+          const int lo = tile_lo(it, 2 * t + h, nk, own, own_off);
           uint32_t sr[64];
-          load_slot(2 * t + h, h, sr);
-          uint32_t pk[32];
-#pragma unroll
-          for (int c = 0; c < 64; c += 4) {
-            const ptx::f32x2 t01 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nr2);
-            const ptx::f32x2 t23 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nr2);
-            float t0, t1, p2, p3;
-            ptx::unpack2(t01, t0, t1);
-            const float p0 = ptx::ex2(t0), p1 = ptx::ex2(t1);
-            const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
-            ptx::unpack2(p23, p2, p3);
-            ps2[0] = ptx::add2(ps2[0], ptx::pack2(p0, p1));
-            ps2[1] = ptx::add2(ps2[1], p23);
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
-            pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
-            pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
+          {
+            uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
+            uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
+            ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN, lo32);
+            ptx::tmem_ld32(tmem_lane + (uint32_t)h * BN + 32, hi32);
+            ptx::tmem_wait_ld(sr);
           }
-          ptx::tmem_st32(tmem_lane + (uint32_t)h * 32, pk);
+          // Visibility.  Slots fully inside the visible region need no masking (the common case).
+          // Ragged tails and the causal diagonal make columns [0, lim) of a row visible; the
+          // 8-column groups below the warp's smallest lim need no masking either, the groups at or
+          // above its largest lim are skipped altogether (their P is zero), and only the groups in
+          // between are masked element by element.  Padded context ranges (reference layout with
+          // gaps between blocks) take the general per-element path.
+          int lim = BN, lim_lo = BN, lim_hi = BN;
+          if (nk < BN || (own && own_off + BN - 1 > it.t0(x)) || (!own && ctx_check)) {
+            lim = nk;
+            if (own) lim = max(0, min(nk, tok - own_off + 1));
+            if (!own && ctx_check) {
+              const unsigned v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
+              const unsigned v1 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + 32 + lane));
+#pragma unroll
+              for (int c = 0; c < 64; ++c) {
+                const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
+                sr[c] = ok ? sr[c] : 0xff800000u;  // -inf
+              }
+            } else {
+              lim_lo = __reduce_min_sync(0xffffffffu, lim);
+              lim_hi = __reduce_max_sync(0xffffffffu, lim);
+            }
+          }
+          // The slot is processed by one of two instantiations: straight-line code when nothing is
+          // masked per group (one basic block: exponentials, polynomial and conversions interleave
+          // freely), or the grouped form with warp-uniform branches around every 8 columns.
+          auto process = [&](auto grouped_tag) {
+            constexpr bool kGrouped = decltype(grouped_tag)::value;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 8) {
+              if (!kGrouped || c0 < lim_hi) {
+                if (kGrouped && c0 + 8 > lim_lo) {
+#pragma unroll
+                  for (int c = c0; c < c0 + 8; ++c) sr[c] = c < lim ? sr[c] : 0xff800000u;  // -inf
+                }
+#pragma unroll
+                for (int c = c0; c < c0 + 8; c += 2)
+                  mx4[(c >> 1) & 3] = ptx::max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+              }
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
+            float m_new = fmaxf(m_run, mx);
+            if (m_run != -INFINITY && m_new - m_run <= kLazy) m_new = m_run;  // keep the old reference: p <= 2^8
+            const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+            const float corr = ptx::ex2(m_run - m_ref);  // 1 when unchanged, 0 on the first visible slot
+            const float neg_ref = -m_ref;
+            const bool changed = m_new != m_run;
+            m_run = m_new;
+
+            if (h == 0 && t > 0) {
+              // previous P V done: O is stable and the P columns (first half of S) may be overwritten
+              wait(kPVDone + x, pv_seen, 32 + x);
+              ++pv_seen;
+              ptx::tc_fence_after_sync();
+            }
+            if ((t > 0 || h > 0) && __any_sync(0xffffffffu, changed)) {
+              // The reference moved by more than the lazy threshold (rare): bring what was accumulated
+              // against the old one in line -- O of the earlier tiles, P of this tile's first slot.
+              if (t > 0) {
+#pragma unroll 1
+                for (int ch = 0; ch < HD / 32; ++ch) {
+                  uint32_t orow[32];
+                  ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+                  ptx::tmem_wait_ld(orow);
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
+                  ptx::tmem_st32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+                }
+              }
+              if (h > 0) {
+                uint32_t p0[32];
+                ptx::tmem_ld32(tmem_lane, p0);
+                ptx::tmem_wait_ld(p0);
+                const __nv_bfloat162 c2 = __float2bfloat162_rn(corr);  // corr is 1 or at most 2^-8: exact enough in bf16
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&p0[i]), c2);
+                  p0[i] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                ptx::tmem_st32(tmem_lane, p0);
+              }
+              ptx::tmem_wait_st();
+            }
+            // p with packed fp32x2 arithmetic.  Every second pair of exponentials is evaluated on the
+            // FMA pipe: the special-function unit (16 results per clock per SM) would otherwise bound
+            // the whole kernel.
+            const ptx::f32x2 sc2 = ptx::pack2(a.scale_log2, a.scale_log2), nr2 = ptx::pack2(neg_ref, neg_ref);
+            ptx::f32x2 ps2[2] = {0ull, 0ull};
+            uint32_t pk[32];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 8) {
+              if (!kGrouped || c0 < lim_hi) {
+#pragma unroll
+                for (int c = c0; c < c0 + 8; c += 4) {
+                  const ptx::f32x2 t01 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nr2);
+                  const ptx::f32x2 t23 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nr2);
+                  float t0, t1, p2, p3;
+                  ptx::unpack2(t01, t0, t1);
+                  const float p0 = ptx::ex2(t0), p1 = ptx::ex2(t1);
+                  const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
+                  ptx::unpack2(p23, p2, p3);
+                  ps2[0] = ptx::add2(ps2[0], ptx::pack2(p0, p1));
+                  ps2[1] = ptx::add2(ps2[1], p23);
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+                  pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+                  pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pk[(c0 >> 1) + i] = 0u;
+              }
+            }
+            ptx::tmem_st32(tmem_lane + (uint32_t)h * 32, pk);
+            float s0, s1, s2, s3;
+            ptx::unpack2(ps2[0], s0, s1);
+            ptx::unpack2(ps2[1], s2, s3);
+            l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
+          };
+          if (lim_hi == BN && lim_lo == BN) process(std::false_type{}); else process(std::true_type{});
         }
-        float s0, s1, s2, s3;
-        ptx::unpack2(ps2[0], s0, s1);
-        ptx::unpack2(ps2[1], s2, s3);
-        l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
         __syncwarp();
@@ -624,15 +721,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ++pv_seen;
       ptx::tc_fence_after_sync();
       __syncwarp();
+      // O leaves tensor memory in four 32-column chunks, software-pipelined: the load of the next
+      // chunk is in flight while the current one is converted and stored.
+      uint32_t obuf[2][32];
+      ptx::tmem_ld32(tmem_lane + kColO, obuf[0]);
       if (it.split) {
         // un-normalised partial (O, max, sum) of this key chunk; merged by attn_combine_kernel
         const bool wr = active && tok < a.lq_max;
         const int64_t prow = (((int64_t)it.b * a.N + n) * a.lq_max + tok) * a.n_split + it.chunk;
-#pragma unroll 1
+#pragma unroll
         for (int ch = 0; ch < HD / 32; ++ch) {
-          uint32_t orow[32];
-          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+          uint32_t (&orow)[32] = obuf[ch & 1];
           ptx::tmem_wait_ld(orow);
+          if (ch + 1 < HD / 32) {
+            ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)(ch + 1) * 32, obuf[(ch + 1) & 1]);
+          } else {  // O is out of TMEM: the next item's first P V may overwrite it
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
+          }
           if (wr) {
             float4* dst = reinterpret_cast<float4*>(a.part_o + prow * HD + ch * 32);
 #pragma unroll
@@ -641,9 +748,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                    __uint_as_float(orow[4 * i + 2]), __uint_as_float(orow[4 * i + 3]));
           }
         }
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
         if (wr) a.part_ml[prow] = make_float2(m_run, l_run);
       } else {
         // O / l -> bf16, stored straight from registers: each thread owns one 256-byte output row
@@ -652,12 +756,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)it.b * a.o.sb +
                                  (int64_t)(it.start + tok) * a.o.ss + (int64_t)n * a.o.sh;
-#pragma unroll 1
+#pragma unroll
         for (int ch = 0; ch < HD / 32; ++ch) {
-          uint32_t orow[32];
-          ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+          uint32_t (&orow)[32] = obuf[ch & 1];
           ptx::tmem_wait_ld(orow);
-          if (ch == HD / 32 - 1) {  // O is out of TMEM: the next item's first P V may overwrite it
+          if (ch + 1 < HD / 32) {
+            ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)(ch + 1) * 32, obuf[(ch + 1) & 1]);
+          } else {  // O is out of TMEM: the next item's first P V may overwrite it
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(kOFree + x));
