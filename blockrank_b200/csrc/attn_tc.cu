@@ -147,6 +147,7 @@ struct TcArgs {
   int o_align32;    // output rows are 32-byte aligned (enables 32-byte stores)
   int total_items;
   FastDiv div_sec1, div_nbg, div_sec2, div_nk;  // by nbg*n_split, nbg, nbg*(M-1), Nk
+  int* work_counter;  // next unclaimed index of the work list (zeroed before the launch)
   float* part_o;    // [B, N, lq_max, n_split, 128] un-normalised partial outputs
   float2* part_ml;  // [B, N, lq_max, n_split] (running max in log2 units, sum)
 };
@@ -398,11 +399,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         ++n_pub;
       };
-      ItemRaw raw_next = load_item(a, blockIdx.x);
+      // The work list (longest items first) is handed out dynamically: whichever CTA is free claims
+      // the next index.  Claims run two items ahead and the block spans of a claimed item one item
+      // ahead, so neither the atomic nor the loads are waited for.
+      auto claim = [&]() {
+        int v = 0;
+        if (leader) v = atomicAdd(a.work_counter, 1);
+        return __shfl_sync(0xffffffffu, v, 0);
+      };
+      int idx = claim(), idx_next = claim();
+      ItemRaw raw_next = load_item(a, idx);
       Item it{};
-      for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+      for (; idx < a.total_items; idx = idx_next, idx_next = claim()) {
         const ItemRaw raw = raw_next;
-        raw_next = load_item(a, idx + gridDim.x);  // in flight while this item is processed
+        raw_next = load_item(a, idx_next);  // in flight while this item is processed
         it = decode_item(a, raw);
         if (!it.valid) continue;
         int flags = it.split ? kRecSplit : 0;
@@ -471,15 +481,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       };
       auto issue_qk = [&](int x, int keys, bool last, uint32_t st) {
         const uint32_t idesc = idesc_qk0 | ((uint32_t)((keys + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
-        const uint64_t ad = q_desc0 + (uint64_t)((uint32_t)x * (kQBytes >> 4));
-        const uint64_t bd = k_desc0 + (uint64_t)(st * (kStageBytes >> 4));
+        const uint32_t a_lo = (uint32_t)q_desc0 + (uint32_t)x * (kQBytes >> 4);
+        const uint32_t b_lo = (uint32_t)k_desc0 + st * (kStageBytes >> 4);
+        const uint32_t a_hi = (uint32_t)(q_desc0 >> 32), b_hi = (uint32_t)(k_desc0 >> 32);
         const uint32_t d = tmem + (uint32_t)x * kChainCols;
         if (leader) {
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks) {
             const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
             const uint32_t boff = (uint32_t)(ks >> 2) * ((BT * 128) >> 4) + (uint32_t)(ks & 3) * 2;
-            ptx::mma_ss(d, ad + aoff, bd + boff, idesc, ks > 0);
+            ptx::mma_ss_lohi(d, a_lo + aoff, a_hi, b_lo + boff, b_hi, idesc, ks > 0);
           }
           ptx::mma_commit(bar(kSFull + x));
           if (last) ptx::mma_commit(bar(kQFree + x));  // last read of this chain's Q tile
@@ -487,13 +498,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       };
       auto issue_pv = [&](int x, int keys, bool first, uint32_t st) {
         const uint32_t pa = tmem + (uint32_t)x * kChainCols;  // P sits over the first 64 columns of S
-        const uint64_t bd = v_desc0 + (uint64_t)(st * (kStageBytes >> 4));
+        const uint32_t b_lo = (uint32_t)v_desc0 + st * (kStageBytes >> 4), b_hi = (uint32_t)(v_desc0 >> 32);
         const uint32_t d = tmem + (uint32_t)x * kChainCols + kColO;
         const int ksteps = (keys + 15) >> 4;
         if (leader) {
 #pragma unroll
           for (int ks = 0; ks < BT / 16; ++ks)
-            if (ks < ksteps) ptx::mma_ts(d, pa + (uint32_t)ks * 8, bd + (uint32_t)ks * ((16 * 128) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
+            if (ks < ksteps)
+              ptx::mma_ts_lohi(d, pa + (uint32_t)ks * 8, b_lo + (uint32_t)ks * ((16 * 128) >> 4), b_hi, idesc_pv, (!first || ks > 0) ? 1u : 0u);
           ptx::mma_commit(bar(kPVDone + x));
         }
       };
@@ -834,8 +846,9 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(TcArgs a) {
 }
 
 // neutral partials for chunks that own no tile (the combine step skips sum == 0)
-__global__ void attn_clear_partials_kernel(float2* ml, int64_t n) {
+__global__ void attn_clear_partials_kernel(float2* ml, int64_t n, int* work_counter) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) *work_counter = 0;
   if (i < n) ml[i] = make_float2(-INFINITY, 0.f);
 }
 
@@ -844,6 +857,8 @@ __global__ void attn_clear_partials_kernel(float2* ml, int64_t n) {
 // Key chunks for the query block.  Its context is every earlier token of the prompt (S is the only
 // bound known on the host), walked 64 keys per step per row tile; cutting it into chunks of about
 // 1024 keys keeps that serial chain short and spreads it over the SMs.
+constexpr size_t kWsHeader = 256;  // workspace: [work counter, padding][partial O][partial (max, sum)]
+
 static int tc_splits(const brk_attn_params& p) {
   if (p.M < 2) return 1;
   int n = (p.S + 1023) / 1024;
@@ -852,9 +867,9 @@ static int tc_splits(const brk_attn_params& p) {
 
 size_t attn_tc_workspace(const brk_attn_params& p) {
   const int ns = tc_splits(p);
-  if (ns <= 1) return 0;
+  if (ns <= 1) return kWsHeader;  // the work counter
   const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
-  return rows * HD * sizeof(float) + rows * sizeof(float2);
+  return kWsHeader + rows * HD * sizeof(float) + rows * sizeof(float2);
 }
 
 int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
@@ -865,7 +880,7 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   BRK_REQUIRE(p.scale > 0.f, BRK_E_ARG, "softmax scale must be positive");
   const int ns = tc_splits(p);
   const size_t need = attn_tc_workspace(p);
-  BRK_REQUIRE(need == 0 || (ws != nullptr && ws_bytes >= need && ((uintptr_t)ws & 15) == 0), BRK_E_WORKSPACE,
+  BRK_REQUIRE(ws != nullptr && ws_bytes >= need && ((uintptr_t)ws & 15) == 0, BRK_E_WORKSPACE,
               "attention workspace: %zu bytes (16-byte aligned) needed, %zu given", need, ws_bytes);
   int gs = 0;
   while ((1 << gs) < G) ++gs;
@@ -908,10 +923,13 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   a.div_sec2 = make_fastdiv((uint32_t)(p.B * p.Nk * (p.M > 1 ? p.M - 1 : 1)));
   a.div_nk = make_fastdiv((uint32_t)p.Nk);
   const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
-  a.part_o = ns > 1 ? reinterpret_cast<float*>(ws) : nullptr;
-  a.part_ml = ns > 1 ? reinterpret_cast<float2*>(reinterpret_cast<float*>(ws) + rows * HD) : nullptr;
-  if (ns > 1) {
-    attn_clear_partials_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(a.part_ml, (int64_t)rows);
+  float* const part = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kWsHeader);
+  a.work_counter = reinterpret_cast<int*>(ws);
+  a.part_o = ns > 1 ? part : nullptr;
+  a.part_ml = ns > 1 ? reinterpret_cast<float2*>(part + rows * HD) : nullptr;
+  {
+    const int64_t n_clear = ns > 1 ? (int64_t)rows : 0;  // always launched: it also resets the work counter
+    attn_clear_partials_kernel<<<(unsigned)(n_clear > 0 ? (n_clear + 255) / 256 : 1), 256, 0, st>>>(a.part_ml, n_clear, a.work_counter);
     BRK_CUDA(cudaGetLastError());
   }
   const int grid = (int)(total_items < sms[dev] ? total_items : sms[dev]);

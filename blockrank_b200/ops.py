@@ -102,7 +102,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, blk_start: torc
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
         _lib.check(L.brk_attn_fwd(C.byref(p), ws.data_ptr() if ws is not None else None, nbytes, _stream(q)),
                    "brk_attn_fwd")
-    _count(3 if nbytes else 1)  # key-chunked query block: clear partials + main kernel + merge
+    # tensor-core path: reset (work counter, partials) + main kernel [+ merge of the key-chunked query block]
+    _count(1 if not nbytes else 3 if nbytes > 256 else 2)
     return (out, lse) if return_lse else out
 
 
