@@ -348,8 +348,8 @@ def run_ours(args):
                      "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": achieved / pk["bf16_tflops_sustained"],
                      # dram__bytes_read+write of one ncu capture on 2 prompts of this geometry (profiles/),
-                     # 476.3 MB per prompt, scaled to the prompts of one launch (traffic grows with prompts)
-                     "traffic": 476.3e6 * micro if args.docs == 100 and args.algo != "simt" else None,
+                     # 471.2 MB per prompt, scaled to the prompts of one launch (traffic grows with prompts)
+                     "traffic": 471.2e6 * micro if args.docs == 100 and args.algo != "simt" else None,
                      "peak_source": pk["source"],
                      "flops_exact_per_launch": f_exact * micro, "launch_ms": attn_avg_s * 1e3,
                      "live_tile_tflops": live, "live_tile_frac": live / pk["bf16_tflops_sustained"],

@@ -1,7 +1,7 @@
 // BlockRank attention forward on the sm_100a tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// Persistent, warp-specialised kernel: one CTA per SM walks a static list of work items.
-// A work item is (prompt b, KV head g, block m, pair of row tiles[, key chunk]); a row tile is
+// Persistent, warp-specialised kernel: one CTA per SM; the CTAs claim work items (longest first)
+// from a global counter.  A work item is (prompt b, KV head g, block m, pair of row tiles[, key chunk]); a row tile is
 // 128 MMA rows = 128/G consecutive query tokens x the G query heads that share KV head g, so
 // one K/V tile in shared memory serves the whole GQA group and a Q tile is one 3-D TMA box of
 // the [B,S,N,D] tensor.  The two row tiles of a pair ("chains") share the item's K/V tiles and
@@ -19,15 +19,16 @@
 //
 // Roles (320 threads):
 //   warps 0-3 / 4-7  softmax + output of chain 0 / 1 (thread = row = TMEM lane)
-//   warp 8           TMA producer: Q tiles and a 2-stage ring of 128-key K/V tiles, running ahead
-//                    across items
+//   warp 8           TMA producer: claims and decodes the items (the decoded item goes to the other
+//                    roles through a 4-deep record ring in shared memory), loads Q tiles and a
+//                    2-stage ring of 128-key K/V tiles, running ahead across items
 //   warp 9           MMA issuer: S = Q K^T (both operands K-major, 128B swizzle) and O += P V
 //                    (P read from tensor memory, V as the MN-major B operand)
 // O stays in TMEM across the key tiles of an item; softmax is base-2, online, with a lazy
 // rescale (O is only touched when the running max grows by more than 2^8).  P (bf16, two keys
 // per 32-bit column) overwrites the first half of the S tile it was computed from.
 //
-// Shared memory 193 KB: Q 2x32 KB, K/V ring 2x64 KB.  TMEM: 2 x (S 128 + O 128) columns.
+// Shared memory 194 KB: Q 2x32 KB, K/V ring 2x64 KB, barriers, item records.  TMEM: 2 x (S 128 + O 128) columns.
 // No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the thread records
 // a code in the caller's status word, stops waiting and runs to the normal exit.
 #include <cuda.h>

@@ -101,6 +101,10 @@ BRK_API int brk_device_check(void);
 BRK_API int brk_spans_from_mask(const uint8_t* mask, int32_t B, int32_t M, int32_t H,
                         int32_t* blk_start, int32_t* blk_len, void* stream);
 
+/* Device scratch the call needs (16-byte aligned; contents need not be initialised or
+ * preserved between calls, but two calls in flight must not share it).  The tensor-core
+ * path always needs some: a work counter, plus the partial results of the query block's
+ * key chunks for long prompts.  The CUDA-core path needs none (0). */
 BRK_API size_t brk_attn_fwd_workspace_bytes(const brk_attn_params* p);
 BRK_API int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
