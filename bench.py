@@ -319,6 +319,7 @@ def run_ours(args):
     score_ms = [a.elapsed_time(b) for a, b in rk.events["score"]]
     rk.events = None
 
+    rk.use_graphs = bool(args.graphs)
     for _ in range(min(args.warmup, 3)):
         step_e2e()
     e2e_ms = timed(step_e2e, args.steps)
@@ -384,6 +385,7 @@ def main():
     ap.add_argument("--micro", type=int, default=4, help="prompts per forward pass")
     ap.add_argument("--algo", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graphs", action="store_true", help="e2e leg replays one captured CUDA graph per forward pass")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

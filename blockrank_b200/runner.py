@@ -47,6 +47,13 @@ class RankerConfig:
                             num_attention_heads=4, num_key_value_heads=2, head_dim=64, score_layer=score_layer)
 
 
+@dataclass
+class _CapturedScore:
+    graph: "torch.cuda.CUDAGraph"
+    static: list   # input buffers the graph reads
+    out: tuple     # (logits, doc_mass) the graph writes
+
+
 class MistralPrefillRanker:
     """Holds the fused weights of layers 0..score_layer on one GPU and ranks prompts."""
 
@@ -61,6 +68,8 @@ class MistralPrefillRanker:
         self.inv_freq = inv.to(self.device)
         self.algo = _lib.ALGO_AUTO
         self.events = None  # set to {"attn": [], "score": []} to collect (start, end) CUDA events per launch
+        self.use_graphs = False  # rank_host replays one captured CUDA graph per batch geometry instead of launching eagerly
+        self._graphs: Dict[tuple, "_CapturedScore"] = {}
 
     # ---- weights ---------------------------------------------------------------
     def load_state_dict(self, sd: Dict[str, torch.Tensor]) -> "MistralPrefillRanker":
@@ -172,6 +181,37 @@ class MistralPrefillRanker:
         self._tock(ev)
         return logits, mass
 
+    # ---- CUDA graphs -----------------------------------------------------------
+    @torch.no_grad()
+    def score_graphed(self, input_ids, position_ids, blk_start, blk_len, max_block_len, signal_rows):
+        """Same contract as :meth:`score`, but the whole launch sequence (about 440 kernels for the 7B
+        architecture) is captured once per batch geometry ``(B, S, M, R, max_block_len)`` and replayed.
+
+        Inputs are copied into the graph's static buffers; the returned tensors are the graph's static
+        outputs and are overwritten by the next call with the same geometry.  The first call for a
+        geometry runs eagerly twice (library initialisation, allocator warm-up) before capturing.
+        """
+        key = (tuple(input_ids.shape), tuple(blk_start.shape), tuple(signal_rows.shape), int(max_block_len))
+        cap = self._graphs.get(key)
+        if cap is None:
+            if self.events is not None:
+                raise RuntimeError("per-launch events cannot be collected while capturing a CUDA graph")
+            static = [t.clone() for t in (input_ids, position_ids, blk_start, blk_len, signal_rows)]
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self.score(static[0], static[1], static[2], static[3], int(max_block_len), static[4])
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.score(static[0], static[1], static[2], static[3], int(max_block_len), static[4])
+            cap = self._graphs[key] = _CapturedScore(graph, static, out)
+        for dst, src in zip(cap.static, (input_ids, position_ids, blk_start, blk_len, signal_rows)):
+            dst.copy_(src, non_blocking=True)
+        cap.graph.replay()
+        return cap.out
+
     def _tick(self, kind):
         if self.events is None:
             return None
@@ -195,7 +235,8 @@ class MistralPrefillRanker:
         pos = batch["position_ids"].to(dev, non_blocking=True)
         spans = batch["block_spans"].to(dev, non_blocking=True)
         rows = batch["signal_rows"].to(dev, non_blocking=True)
-        logits, _ = self.score(ids, pos, spans[0], spans[1], int(batch["max_block_len"]), rows)
+        run = self.score_graphed if self.use_graphs else self.score
+        logits, _ = run(ids, pos, spans[0], spans[1], int(batch["max_block_len"]), rows)
         top = torch.topk(logits, k=min(k, logits.shape[-1]), dim=-1).indices
         return logits.cpu(), top.cpu()
 

@@ -180,3 +180,27 @@ def test_runner_packed_equals_padded():
         prow[b, 0], prow[b, 1] = idx.numel() - 2, idx.numel() - 1
     lq, _ = rk.score(ids.cuda(), pos.cuda(), ps.cuda(), pl.cuda(), mbl, prow.cuda())
     assert torch.allclose(lp, lq, rtol=1e-4), (lp, lq)
+
+
+def test_runner_graph_replay_equals_eager():
+    """The captured CUDA graph of the scoring pass gives the eager result, also when replayed on new
+    inputs of the same geometry (bf16, tensor-core attention: head_dim 128, N/Nk = 4)."""
+    cfg = RankerConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
+                       num_attention_heads=4, num_key_value_heads=1, head_dim=128, score_layer=2)
+    rk = MistralPrefillRanker(cfg, "cuda", dtype=torch.bfloat16).init_random(seed=5)
+    blens = [[24, 40, 33, 64, 17, 20], [16, 64, 50, 9, 31, 12]]
+    ps, pl, Sp, mbl = H_.packed_spans(blens)
+    B = len(blens)
+    g = torch.Generator().manual_seed(11)
+    rows = torch.tensor([[sum(bl) - 2, sum(bl) - 1] for bl in blens], dtype=torch.int32).cuda()
+    outs = []
+    for trial in range(2):
+        ids = torch.randint(3, 1024, (B, Sp), generator=g).cuda()
+        pos = torch.arange(Sp).expand(B, Sp).contiguous().cuda()
+        eager, _ = rk.score(ids, pos, ps.cuda(), pl.cuda(), mbl, rows)
+        graphed, _ = rk.score_graphed(ids, pos, ps.cuda(), pl.cuda(), mbl, rows)
+        torch.cuda.synchronize()
+        assert torch.equal(eager, graphed.clone()), (trial, (eager - graphed).abs().max())
+        outs.append(eager.clone())
+    assert len(rk._graphs) == 1            # one geometry, one capture
+    assert not torch.equal(outs[0], outs[1])  # the replay really saw the new tokens
