@@ -204,3 +204,26 @@ def test_runner_graph_replay_equals_eager():
         outs.append(eager.clone())
     assert len(rk._graphs) == 1            # one geometry, one capture
     assert not torch.equal(outs[0], outs[1])  # the replay really saw the new tokens
+
+
+def test_rank_items_matches_score_topk():
+    """metrics.rank_items (collate -> rank_host -> top-k lists) against the same prompts scored directly."""
+    from blockrank_b200 import metrics
+    from blockrank_b200.collate import packed_block_collate_fn
+    cfg = RankerConfig.tiny(score_layer=2)
+    rk = MistralPrefillRanker(cfg, "cuda", dtype=torch.float32).init_random(seed=7)
+    g = torch.Generator().manual_seed(21)
+    items = []
+    for _ in range(3):
+        bl = [12] + [int(x) for x in torch.randint(5, 30, (12,), generator=g)] + [9]  # instruction, 12 docs, query
+        items.append({"input_ids": torch.randint(3, 32768, (sum(bl) + 1,), generator=g),
+                      "block_lengths": torch.tensor(bl + [1])})                          # completion = last token
+    preds = metrics.rank_items(rk, items, batch_size=2, k=5)
+    assert len(preds) == 3 and all(len(p) == 5 for p in preds)
+    for i, it in enumerate(items):
+        b = packed_block_collate_fn([it])
+        logits, _ = rk.score(b["input_ids"].cuda(), b["position_ids"].cuda(), b["block_spans"][0].cuda(),
+                             b["block_spans"][1].cuda(), b["max_block_len"], b["signal_rows"].cuda())
+        assert preds[i] == torch.topk(logits[0], 5).indices.tolist()
+    m = metrics.ranking_metrics(preds, [p[0] for p in preds])
+    assert m["accuracy"] == 100.0
