@@ -5,11 +5,18 @@
 //                        owns whole key rows (read once per KV head, shared by
 //                        the G query heads of the group) and keeps an online
 //                        (max, sum-exp) per signal row; the CTA writes one
-//                        (max, sum) pair per (head, row, document).
-//   doc_finalize_kernel  one warp per (prompt, head, row): merges the
+//                        (max, sum) pair per (head, row, document).  fp32 inputs.
+//   doc_partial_mma_kernel  the same for bf16: the (G*R signal rows) x (keys)
+//                        products go through warp-level mma (m16n8k16), key
+//                        rows straight from global memory into the B fragments.
+//                        The product is 8-16 rows tall and bound by the K read;
+//                        a tcgen05 tile (M >= 64, operands staged in shared
+//                        memory, result through tensor memory) would add
+//                        latency to a kernel that has no tensor-rate problem.
+//   doc_finalize_kernel  one CTA per prompt, one warp per (head, row): merges the
 //                        per-document pairs into the softmax over all document
-//                        tokens and emits the per-document probability mass.
-//   doc_logits_kernel    mean over heads and rows / temperature.
+//                        tokens and emits the per-document probability mass,
+//                        then the mean over heads and rows / temperature.
 //   raw_scores_kernel    compatibility output: raw masked logits of the last R
 //                        slots against every slot.
 #include "brk_common.cuh"
@@ -151,35 +158,132 @@ __global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
   }
 }
 
-// One warp per (prompt, head, signal row): softmax over all documents from the per-document pairs.
-__global__ void __launch_bounds__(128) doc_finalize_kernel(const float2* __restrict__ partial, float* __restrict__ mass,
-                                                           int total_rows, int nd) {
-  const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (w >= total_rows) return;
-  const float2* p = partial + (size_t)w * nd;
-  float mx = -INFINITY;
-  for (int d = lane; d < nd; d += 32) mx = fmaxf(mx, p[d].x);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  const float ref = (mx == -INFINITY) ? 0.f : mx;
-  float z = 0.f;
-  for (int d = lane; d < nd; d += 32) z += p[d].y * exp2f(p[d].x - ref);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
-  const float inv = z > 0.f ? 1.f / z : 0.f;
-  for (int d = lane; d < nd; d += 32) mass[(size_t)w * nd + d] = p[d].y * exp2f(p[d].x - ref) * inv;
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// logits[b, d] = mean over (head, row) of mass / temperature; one thread per document, fixed order.
-__global__ void __launch_bounds__(128) doc_logits_kernel(const float* __restrict__ mass, float* __restrict__ logits,
-                                                         int NR, int nd, float inv_count_temp) {
-  const int b = blockIdx.y, d = blockIdx.x * 128 + threadIdx.x;
-  if (d >= nd) return;
-  const float* p = mass + (size_t)b * NR * nd + d;
-  float acc = 0.f;
-  for (int i = 0; i < NR; ++i) acc += p[(size_t)i * nd];
-  logits[(size_t)b * nd + d] = acc * inv_count_temp;
+// bf16 version of doc_partial_kernel on warp-level MMA.  One CTA per (document, prompt, KV head);
+// a warp takes 8 keys at a time: C[16 signal rows x 8 keys] += Q[16 x 16] K^T[16 x 8] over D/16
+// steps.  Lane (q = lane/4, j = lane%4) reads 16 bytes (8 elements of d) of key q per 32 elements
+// of d, which is exactly its B fragment for two consecutive k-steps when the contraction index is
+// taken in the order (8j+0,1 | 8j+2,3) then (8j+4,5 | 8j+6,7); the A fragments (signal rows q and
+// q+8) are read from Q with the same 16-byte pattern, so both operands come straight from global
+// memory with fully used sectors and no shared-memory staging.
+template <int D>
+__global__ void __launch_bounds__(kThreads) doc_partial_mma_kernel(ScoreArgs a) {
+  constexpr int kSteps = D / 32;
+  __shared__ float2 red[kThreads / 32][16];
+  const int G = a.N / a.Nk;
+  const int GR = G * a.R;
+  const int nd = a.M - 2;
+  const int d = blockIdx.x;
+  const int b = blockIdx.y / a.Nk, g = blockIdx.y % a.Nk;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qr = lane >> 2, j = lane & 3;
+  const int start = a.blk_start[(size_t)b * a.M + 1 + d];
+  const int len = a.blk_len[(size_t)b * a.M + 1 + d];
+  const float sl2 = a.scale * 1.4426950408889634f;
+  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)g * a.k.sh;
+
+  for (int r0 = 0; r0 < GR; r0 += 16) {
+    uint4 qa[kSteps], qb[kSteps];  // signal rows r0+qr and r0+qr+8
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = r0 + qr + 8 * h;
+      const bool ok = row < GR;
+      const int hl = ok ? row / a.R : 0, r = ok ? row % a.R : 0;
+      const int slot = a.rows[b * a.R + r];
+      const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(a.q.ptr) + (int64_t)b * a.q.sb +
+                                (int64_t)(g * G + hl) * a.q.sh + (int64_t)slot * a.q.ss + 8 * j;
+#pragma unroll
+      for (int st = 0; st < kSteps; ++st) {
+        const uint4 v = ok ? *reinterpret_cast<const uint4*>(qp + 32 * st) : make_uint4(0, 0, 0, 0);
+        if (h == 0) qa[st] = v; else qb[st] = v;
+      }
+    }
+    float m_lo = -INFINITY, l_lo = 0.f, m_hi = -INFINITY, l_hi = 0.f;
+    for (int base = warp * 8; base < len; base += (kThreads / 32) * 8) {
+      const int key = min(base + qr, len - 1);  // rows past the end re-read the last key; their columns are dropped below
+      const __nv_bfloat16* kp = kbase + (int64_t)(start + key) * a.k.ss + 8 * j;
+      uint4 kf[kSteps];
+#pragma unroll
+      for (int st = 0; st < kSteps; ++st) kf[st] = *reinterpret_cast<const uint4*>(kp + 32 * st);
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int st = 0; st < kSteps; ++st) {
+        mma_bf16_16x8x16(c, qa[st].x, qb[st].x, qa[st].y, qb[st].y, kf[st].x, kf[st].y);
+        mma_bf16_16x8x16(c, qa[st].z, qb[st].z, qa[st].w, qb[st].w, kf[st].z, kf[st].w);
+      }
+      // c[0], c[1]: row qr, keys base + 2j, 2j + 1; c[2], c[3]: row qr + 8, same keys
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (base + 2 * j + e < len) {
+          merge_ml(m_lo, l_lo, c[e] * sl2, 1.f);
+          merge_ml(m_hi, l_hi, c[2 + e] * sl2, 1.f);
+        }
+      }
+    }
+    // the four lanes of a row, then the warps, in a fixed order
+#pragma unroll
+    for (int off = 1; off <= 2; off <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m_lo, off), l2 = __shfl_xor_sync(0xffffffffu, l_lo, off);
+      merge_ml(m_lo, l_lo, m2, l2);
+      const float m3 = __shfl_xor_sync(0xffffffffu, m_hi, off), l3 = __shfl_xor_sync(0xffffffffu, l_hi, off);
+      merge_ml(m_hi, l_hi, m3, l3);
+    }
+    __syncthreads();  // red[] of the previous row batch has been read
+    if (j == 0) {
+      red[warp][qr] = make_float2(m_lo, l_lo);
+      red[warp][qr + 8] = make_float2(m_hi, l_hi);
+    }
+    __syncthreads();
+    if (tid < 16 && r0 + tid < GR) {
+      float mm = -INFINITY, ll = 0.f;
+      for (int w = 0; w < kThreads / 32; ++w) merge_ml(mm, ll, red[w][tid].x, red[w][tid].y);
+      const int row = r0 + tid;
+      const int n = g * G + row / a.R, r = row % a.R;
+      a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
+    }
+  }
 }
+
+// One CTA per prompt.  Phase 1, one warp per (head, signal row) at a time: merge the per-document
+// (max, sum) pairs into the softmax over all document tokens and emit the per-document probability
+// mass.  Phase 2 (when logits are wanted), one thread per document: mean over heads and rows of the
+// masses this CTA has just written, divided by the temperature, summed in a fixed order.
+__global__ void __launch_bounds__(1024) doc_finalize_kernel(const float2* __restrict__ partial, float* __restrict__ mass,
+                                                            float* __restrict__ logits, int NR, int nd,
+                                                            float inv_count_temp) {
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int row = warp; row < NR; row += nwarps) {
+    const size_t w = (size_t)b * NR + row;
+    const float2* p = partial + w * nd;
+    float mx = -INFINITY;
+    for (int d = lane; d < nd; d += 32) mx = fmaxf(mx, p[d].x);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    const float ref = (mx == -INFINITY) ? 0.f : mx;
+    float z = 0.f;
+    for (int d = lane; d < nd; d += 32) z += p[d].y * exp2f(p[d].x - ref);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
+    const float inv = z > 0.f ? 1.f / z : 0.f;
+    for (int d = lane; d < nd; d += 32) mass[w * nd + d] = p[d].y * exp2f(p[d].x - ref) * inv;
+  }
+  if (logits == nullptr) return;
+  __syncthreads();  // the masses of this prompt, written by this CTA, are visible to all its threads
+  for (int d = threadIdx.x; d < nd; d += blockDim.x) {
+    const float* p = mass + (size_t)b * NR * nd + d;
+    float acc = 0.f;
+    for (int i = 0; i < NR; ++i) acc += p[(size_t)i * nd];
+    logits[(size_t)b * nd + d] = acc * inv_count_temp;
+  }
+}
+
 
 // block index of a slot, or -1 for padding (blk_start is non-decreasing)
 __device__ __forceinline__ int block_of(const int32_t* bs, const int32_t* bl, int M, int s) {
@@ -291,17 +395,19 @@ int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cuda
     BRK_CUDA(cudaGetLastError());
     return BRK_OK;
   };
-  if (p.dtype == BRK_BF16) rc = p.D == 128 ? launch(doc_partial_kernel<__nv_bfloat16, 128>) : launch(doc_partial_kernel<__nv_bfloat16, 64>);
-  else rc = p.D == 128 ? launch(doc_partial_kernel<float, 128>) : launch(doc_partial_kernel<float, 64>);
-  if (rc) return rc;
-  const int total_rows = p.B * p.N * p.R;
-  doc_finalize_kernel<<<(total_rows + 3) / 4, 128, 0, st>>>(a.partial, p.doc_mass, total_rows, nd);
-  BRK_CUDA(cudaGetLastError());
-  if (p.logits != nullptr) {
-    doc_logits_kernel<<<dim3((nd + 127) / 128, p.B), 128, 0, st>>>(p.doc_mass, p.logits, p.N * p.R, nd,
-                                                                    1.f / ((float)(p.N * p.R) * p.temperature));
+  if (p.dtype == BRK_BF16) {
+    if (p.D == 128) doc_partial_mma_kernel<128><<<grid, kThreads, 0, st>>>(a);
+    else doc_partial_mma_kernel<64><<<grid, kThreads, 0, st>>>(a);
     BRK_CUDA(cudaGetLastError());
+  } else {
+    rc = p.D == 128 ? launch(doc_partial_kernel<float, 128>) : launch(doc_partial_kernel<float, 64>);
   }
+  if (rc) return rc;
+  const int NR = p.N * p.R;
+  const int fin_threads = NR >= 32 ? 1024 : NR * 32;  // one warp per (head, row), 32 warps at most
+  doc_finalize_kernel<<<p.B, fin_threads, 0, st>>>(a.partial, p.doc_mass, p.logits, NR, nd,
+                                                   1.f / ((float)NR * p.temperature));
+  BRK_CUDA(cudaGetLastError());
   return BRK_OK;
 }
 

@@ -143,7 +143,7 @@ def doc_scores(q: torch.Tensor, k: torch.Tensor, blk_start: torch.Tensor, blk_le
         nbytes = L.brk_doc_scores_workspace_bytes(C.byref(p))
         ws = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=q.device)
         _lib.check(L.brk_doc_scores(C.byref(p), ws.data_ptr(), nbytes, _stream(q)), "brk_doc_scores")
-    _count(3)
+    _count(2)  # per-document partials + per-prompt finalize (masses and logits)
     return mass, logits
 
 
