@@ -516,6 +516,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (flags & kRecStop) break;
         const int n0 = it.n_0, n1 = it.n_1;
         const int T0 = (n0 + 1) >> 1, T1 = (n1 + 1) >> 1, T = (it.n_tiles + 1) >> 1;
+        // Every tile but a chain's last spans 128 keys (a short context slot inside a tile is masked by
+        // the softmax, not trimmed); the last one is computed once here, off the per-tile path.
+        const int last_keys0 = T0 > 0 ? tile_keys(it, T0 - 1, n0) : 0, last_keys1 = T1 > 0 ? tile_keys(it, T1 - 1, n1) : 0;
+        auto keys_of = [&](int x, int t) { return t + 1 < (x == 0 ? T0 : T1) ? BT : (x == 0 ? last_keys0 : last_keys1); };
 #pragma unroll
         for (int x = 0; x < 2; ++x)
           if ((x == 0 ? n0 : n1) > 0) { wait(kQFull + x, q_uses[x], 20 + x); ++q_uses[x]; }
@@ -530,25 +534,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          const int nx = x == 0 ? n0 : n1, Tx = x == 0 ? T0 : T1;
-          if (Tx > 0) issue_qk(x, tile_keys(it, 0, nx), Tx == 1, kv_cnt % kStages);
+          const int Tx = x == 0 ? T0 : T1;
+          if (Tx > 0) issue_qk(x, keys_of(x, 0), Tx == 1, kv_cnt % kStages);
         }
         for (int t = 0; t < T; ++t) {
           const uint32_t st = (kv_cnt + (uint32_t)t) % kStages;
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            const int nx = x == 0 ? n0 : n1, Tx = x == 0 ? T0 : T1;
+            const int Tx = x == 0 ? T0 : T1;
             if (t >= Tx) continue;
             wait(kPFull + x, p_seen[x], 24 + x);
             ++p_seen[x];
             if (t == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
             ptx::tc_fence_after_sync();
-            issue_pv(x, tile_keys(it, t, nx), t == 0, st);
+            issue_pv(x, keys_of(x, t), t == 0, st);
             if (t + 1 < Tx) {
               // the chain's next S tile: queued behind the P V that reads P out of the same columns
               need_kv(t + 1);
               ptx::tc_fence_after_sync();
-              issue_qk(x, tile_keys(it, t + 1, nx), t + 2 == Tx, (kv_cnt + (uint32_t)t + 1) % kStages);
+              issue_qk(x, keys_of(x, t + 1), t + 2 == Tx, (kv_cnt + (uint32_t)t + 1) % kStages);
             }
           }
           if (leader) ptx::mma_commit(bar(kKVFree + st));  // both chains' MMAs on this stage are queued

@@ -113,6 +113,27 @@ def test_attention_tc_vs_oracle(case):
     assert out.float().cpu()[~rows].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("algo", [SIMT, TC])
+def test_attention_large_logit_range(algo):
+    """Logits spread over tens of units (queries scaled up): the running maximum jumps by more than the
+    lazy-rescale threshold between key slots, so the paths that rescale O -- and, inside a 128-key tile,
+    the P already written for its first slot -- are exercised; the softmax is nearly one-hot."""
+    B, N, Nk, D, M, H = 1, 8, 2, 128, 5, 160
+    lens = H_.random_lens(B, M, H, 31)
+    lens[0][0], lens[0][-1] = 150, 130      # several key slots in the prefix and in the query block
+    mask = H_.ragged_mask(B, M, H, lens)
+    q, k, v = H_.qkv(B, N, Nk, M * H, D, 131, torch.bfloat16)
+    q = (q.float() * 32).to(torch.bfloat16)
+    out, lse = _run_attn(q, k, v, mask, D ** -0.5, algo, lse=True)
+    ref, ref_lse = orc.attention_dense(q, k, v, mask, D ** -0.5)
+    rows = mask.reshape(B, -1)
+    assert torch.isfinite(out.float()).all()
+    err = (out.float().cpu() - ref.float())[rows].abs().max().item()
+    assert err < 3e-2, err
+    lrows = rows[:, None, :].expand(B, N, M * H)
+    assert (lse.cpu() - ref_lse.float())[lrows].abs().max().item() < 2e-2
+
+
 def test_attention_tc_matches_simt_full_blocks():
     """Uniform full blocks at the standalone-op geometry (one prompt): both kernels, same inputs."""
     B, N, Nk, D = 1, 32, 8, 128
