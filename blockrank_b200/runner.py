@@ -120,8 +120,11 @@ class MistralPrefillRanker:
     # ---- forward ---------------------------------------------------------------
     @torch.no_grad()
     def hidden_before_score_layer(self, input_ids, position_ids, blk_start, blk_len, max_block_len):
-        """Run layers 0..l*-1; returns (residual stream h, pending branch output d) so that the
-        scoring layer can fuse the last residual add with its RMSNorm.  Shapes (B*S, hidden)."""
+        """Run layers 0..l*-1; returns the residual stream entering layer l*, shape (B*S, hidden).
+
+        Both residual additions of a layer happen in the epilogue of the GEMM that produces the branch
+        (``h.addmm_``: C = C + A·B, added in fp32 before the rounding), so the branch output is never
+        written to memory and the RMSNorm that follows reads one tensor instead of two."""
         c = self.cfg
         B, S = input_ids.shape
         N, Nk, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
@@ -130,11 +133,9 @@ class MistralPrefillRanker:
         pos = position_ids.reshape(T).to(torch.int32)
         h = torch.embedding(self.embed, input_ids.reshape(T))
         scale = D ** -0.5
-        pending = None  # MLP output not yet added to h
         for i in range(c.score_layer):
             L = self.layers[i]
-            x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps) if pending is None else \
-                ops.rmsnorm(pending, L["ln1"], c.rms_norm_eps, residual=h)
+            x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps)
             qkv = torch.matmul(x, L["wqkv"].t())                         # (T, qd + 2 kd)
             q3 = qkv[:, :qd].view(T, N, D)
             k3 = qkv[:, qd:qd + kd].view(T, Nk, D)
@@ -145,11 +146,11 @@ class MistralPrefillRanker:
             ev = self._tick("attn")
             attn = ops.attention(q4, k4, v4, blk_start, blk_len, scale, max_block_len, algo=self.algo)
             self._tock(ev)
-            o = torch.matmul(attn.view(T, qd), L["wo"].t())
-            x = ops.rmsnorm(o, L["ln2"], c.rms_norm_eps, residual=h)    # h += o
+            h.addmm_(attn.view(T, qd), L["wo"].t())                      # h += o_proj(attn)
+            x = ops.rmsnorm(h, L["ln2"], c.rms_norm_eps)
             act = ops.silu_mul(torch.matmul(x, L["wgu"].t()))
-            pending = torch.matmul(act, L["wd"].t())
-        return h, pending
+            h.addmm_(act, L["wd"].t())                                   # h += down_proj(act)
+        return h
 
     @torch.no_grad()
     def score(self, input_ids, position_ids, blk_start, blk_len, max_block_len, signal_rows):
@@ -161,10 +162,9 @@ class MistralPrefillRanker:
         B, S = input_ids.shape
         N, Nk, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         R = signal_rows.shape[1]
-        h, pending = self.hidden_before_score_layer(input_ids, position_ids, blk_start, blk_len, max_block_len)
+        h = self.hidden_before_score_layer(input_ids, position_ids, blk_start, blk_len, max_block_len)
         L = self.layers[c.score_layer]
-        x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps) if pending is None else \
-            ops.rmsnorm(pending, L["ln1"], c.rms_norm_eps, residual=h)
+        x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps)
         T = B * S
         pos = position_ids.reshape(T).to(torch.int32)
         k = torch.matmul(x, L["wk"].t()).view(T, Nk, D)
