@@ -65,6 +65,50 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, T
   }
 }
 
+// Register-resident variant for hidden = 16 * blockDim.x (4096 -> 256 threads): every thread keeps its 16
+// elements of the row in registers between the sum of squares and the scaling, with 16-byte accesses
+// and no shared-memory staging of the row.  Same arithmetic and rounding points as rmsnorm_kernel.
+template <typename T>
+__global__ void __launch_bounds__(1024) rmsnorm_reg_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                                                           const T* __restrict__ w, T* __restrict__ out, int hidden,
+                                                           float eps) {
+  __shared__ float red[32];
+  const int64_t r = blockIdx.x;
+  const int i = threadIdx.x * 16;
+  const T* xp = x + r * hidden + i;
+  float v[16];
+  load8(xp, *reinterpret_cast<float (*)[8]>(&v[0]));
+  load8(xp + 8, *reinterpret_cast<float (*)[8]>(&v[8]));
+  if (residual) {
+    T* rp = residual + r * hidden + i;
+    float h[16];
+    load8(rp, *reinterpret_cast<float (*)[8]>(&h[0]));
+    load8(rp + 8, *reinterpret_cast<float (*)[8]>(&h[8]));
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = Elem<T>::round(v[j] + h[j]);
+    store8(rp, *reinterpret_cast<float (*)[8]>(&v[0]));
+    store8(rp + 8, *reinterpret_cast<float (*)[8]>(&v[8]));
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) ss += v[j] * v[j];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int j = 0; j < (int)(blockDim.x >> 5); ++j) tot += red[j];
+  const float rs = rsqrtf(tot / (float)hidden + eps);
+  float g[16];
+  load8(w + i, *reinterpret_cast<float (*)[8]>(&g[0]));
+  load8(w + i + 8, *reinterpret_cast<float (*)[8]>(&g[8]));
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = g[j] * Elem<T>::round(v[j] * rs);
+  T* op = out + r * hidden + i;
+  store8(op, *reinterpret_cast<float (*)[8]>(&v[0]));
+  store8(op + 8, *reinterpret_cast<float (*)[8]>(&v[8]));
+}
+
 // ---- RoPE ---------------------------------------------------------------------
 // One thread per (row, 8 rotation pairs): the 8 angles are evaluated once and applied to every
 // query and key head of that row, with 16-byte loads and stores of both halves of each head.
@@ -144,6 +188,17 @@ int spans_launch(const uint8_t* mask, int B, int M, int H, int32_t* start, int32
 
 int rmsnorm_launch(int dtype, const void* x, void* residual, const void* w, void* out, int64_t rows, int hidden,
                    float eps, cudaStream_t st) {
+  if (hidden % 512 == 0 && hidden / 16 <= 1024) {  // whole warps of 16-element threads
+    const int threads = hidden / 16;
+    if (dtype == BRK_BF16)
+      rmsnorm_reg_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)residual,
+                                                                          (const __nv_bfloat16*)w, (__nv_bfloat16*)out, hidden, eps);
+    else
+      rmsnorm_reg_kernel<float><<<(unsigned)rows, threads, 0, st>>>((const float*)x, (float*)residual, (const float*)w,
+                                                                  (float*)out, hidden, eps);
+    BRK_CUDA(cudaGetLastError());
+    return BRK_OK;
+  }
   const size_t sm = (size_t)hidden * 4;
   if (dtype == BRK_BF16) {
     if (sm > 48 * 1024)

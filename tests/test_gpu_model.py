@@ -21,12 +21,13 @@ def _load(golden_dir, name):
     return {k: z[k] for k in z.files}
 
 
+@pytest.mark.parametrize("hidden", [256, 1024, 4096])  # 256: row staged in shared memory; 1024, 4096: register-resident rows
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_rmsnorm(dt):
+def test_rmsnorm(dt, hidden):
     g = torch.Generator().manual_seed(0)
-    x = torch.randn(37, 256, generator=g).to(dt)
-    h = torch.randn(37, 256, generator=g).to(dt)
-    w = (1 + 0.1 * torch.randn(256, generator=g)).to(dt)
+    x = torch.randn(37, hidden, generator=g).to(dt)
+    h = torch.randn(37, hidden, generator=g).to(dt)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dt)
     out = ops.rmsnorm(x.cuda(), w.cuda(), 1e-5).cpu()
     ref = orc.rms_norm(x, w, 1e-5)
     tol = 2e-2 if dt == torch.bfloat16 else 1e-5
