@@ -240,6 +240,34 @@ def test_error_codes():
         ops.spans_from_mask(mask)
 
 
+def test_tc_attention_needs_its_workspace():
+    """The tensor-core path reports a workspace size and refuses to run without it (status, no launch)."""
+    import ctypes as C
+    B, N, Nk, D, M, H = 1, 4, 1, 128, 3, 64
+    mask = H_.ragged_mask(B, M, H, [[64, 40, 30]])
+    q, k, v = (H_.to_cuda_view(t) for t in H_.qkv(B, N, Nk, M * H, D, 3, torch.bfloat16))
+    start, ln = _spans_cuda(mask)
+    out = torch.empty(B, M * H, N, D, dtype=torch.bfloat16, device="cuda")
+    p = _lib.AttnParams()
+    p.dtype, p.algo = 0, TC
+    p.B, p.N, p.Nk, p.D, p.S, p.M, p.max_block_len, p.scale = B, N, Nk, D, M * H, M, H, D ** -0.5
+    p.q, p.k, p.v, p.o = ops._view(q), ops._view(k), ops._view(v), ops._view(out.permute(0, 2, 1, 3))
+    p.lse, p.status = None, None
+    p.blk_start, p.blk_len = start.data_ptr(), ln.data_ptr()
+    L = _lib.lib()
+    need = L.brk_attn_fwd_workspace_bytes(C.byref(p))
+    assert need >= 256
+    rc = L.brk_attn_fwd(C.byref(p), None, 0, None)
+    assert rc == -3 and b"workspace" in L.brk_last_error()
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    assert L.brk_attn_fwd(C.byref(p), ws.data_ptr(), need - 1, None) == -3
+    assert L.brk_attn_fwd(C.byref(p), ws.data_ptr(), need, None) == 0
+    torch.cuda.synchronize()
+    ref, _ = orc.attention_dense(q.cpu(), k.cpu(), v.cpu(), mask, D ** -0.5)
+    rows = mask.reshape(B, -1)
+    assert (out.float().cpu() - ref.float())[rows].abs().max().item() < 2e-2
+
+
 def test_standalone_op_config_parity():
     """BASELINE config 2: B4, 32/8 heads, D128, 64 + 20x160 + 48 tokens, bf16; O and [4,32,20] scores."""
     B, N, Nk, D = 4, 32, 8, 128
