@@ -11,8 +11,8 @@ library; the first call that needs it does, and fails loudly if it is missing.
 from .attention import (ATTN_NAME, BlockSpans, cuda_blockrank_attention_forward, cuda_blockrank_attention_mask,
                         register_cuda_blockrank_attention)
 from .collate import block_icr_collate_fn, packed_block_collate_fn
-from .scores import doc_logits_from_mass, signal_rows_from_labels, topk_documents
+from .scores import doc_logits_from_mass, notebook_scores, signal_rows_from_labels, topk_documents
 
 __all__ = ["ATTN_NAME", "BlockSpans", "cuda_blockrank_attention_forward", "cuda_blockrank_attention_mask",
            "register_cuda_blockrank_attention", "block_icr_collate_fn", "packed_block_collate_fn",
-           "doc_logits_from_mass", "signal_rows_from_labels", "topk_documents"]
+           "doc_logits_from_mass", "notebook_scores", "signal_rows_from_labels", "topk_documents"]

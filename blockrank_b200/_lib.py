@@ -9,8 +9,7 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-# BLOCKRANK_B200_LIB points at an alternative build of the same ABI (e.g. an instrumented one)
-LIB_PATH = os.environ.get("BLOCKRANK_B200_LIB") or os.path.join(PKG, "libblockrank_b200.so")
+LIB_PATH = os.path.join(PKG, "libblockrank_b200.so")
 
 BRK_BF16, BRK_F32 = 0, 1
 ALGO_AUTO, ALGO_SIMT, ALGO_TC = 0, 1, 2

@@ -127,8 +127,13 @@ def packed_block_collate_fn(batch: Sequence[dict], tok=None, max_block_length: O
             spans[0, b, m], spans[1, b, m] = off_dst, k
             if m == M - 1:
                 first = off_dst + (n - comp)
-                if first < off_dst + k:
-                    labels[b, first:off_dst + k] = ids[b, first:off_dst + k]
+                # the two signal rows must lie inside the (possibly truncated) query block; the reference
+                # asserts the same where it looks for the first labelled token (losses.py:43-48)
+                if comp < 1 or first - 1 < off_dst or first >= off_dst + k:
+                    raise ValueError(
+                        f"item {b}: the completion's first token is not inside the kept query block "
+                        f"(block length {n}, kept {k}, completion length {comp}): no signal rows")
+                labels[b, first:off_dst + k] = ids[b, first:off_dst + k]
                 rows[b, 0], rows[b, 1] = first - 1, first
             off_src += n
             off_dst += k

@@ -27,6 +27,13 @@ def doc_logits_from_mass(mass: torch.Tensor, temperature: float = 0.05) -> torch
     return mass.mean(dim=(1, 2)) / temperature
 
 
+def notebook_scores(mass: torch.Tensor) -> torch.Tensor:
+    """The quickstart notebook's scorer (quickstart.ipynb, cell 9): last signal row only, softmax over the
+    document columns, summed per document, mean over heads.  ``mass`` (B, N, R, num_docs) already holds
+    that per-row, per-head document mass, so this is its last row averaged over heads -> (B, num_docs)."""
+    return mass[:, :, -1, :].mean(dim=1)
+
+
 def topk_documents(logits: torch.Tensor, k: int = 10) -> torch.Tensor:
     """scripts/eval_attn.py:150-151."""
     return torch.topk(logits, k=min(k, logits.shape[-1]), dim=-1).indices

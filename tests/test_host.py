@@ -9,7 +9,8 @@ import numpy as np
 import pytest
 import torch
 
-from blockrank_b200 import _lib, block_icr_collate_fn, packed_block_collate_fn, signal_rows_from_labels
+from blockrank_b200 import (_lib, block_icr_collate_fn, notebook_scores, packed_block_collate_fn,
+                            signal_rows_from_labels)
 from blockrank_b200.parallel import gather_scores, partition_prompts
 from oracle import blockrank_oracle as orc
 
@@ -100,6 +101,33 @@ def test_signal_rows_follow_reference_rule():
     bad[0, -16:] = 3  # first labelled token sits at window index 0: the reference asserts here too
     with pytest.raises(ValueError):
         signal_rows_from_labels(bad)
+
+
+def test_packed_collator_refuses_prompts_without_signal_rows():
+    """A completion cut off by truncation, or an empty one, leaves no signal rows: the packed collator
+    raises where the reference asserts 'Bracket token not found' (losses.py:43-48)."""
+    ids = torch.arange(3, 3 + 30)
+    ok = {"input_ids": ids, "block_lengths": torch.tensor([8, 8, 12, 2])}
+    out = packed_block_collate_fn([ok])
+    assert out["signal_rows"].tolist() == [[27, 28]]
+    with pytest.raises(ValueError, match="no signal rows"):   # query block 14 tokens, kept 10: completion cut
+        packed_block_collate_fn([ok], max_block_length=10)
+    with pytest.raises(ValueError, match="no signal rows"):   # empty completion
+        packed_block_collate_fn([{"input_ids": ids, "block_lengths": torch.tensor([8, 8, 14, 0])}])
+
+
+def test_notebook_scores_is_last_row_head_mean():
+    """quickstart.ipynb cell 9: softmax of the last query row over the document columns, summed per
+    document, averaged over heads -- here restated from raw logits and compared with the helper."""
+    g = torch.Generator().manual_seed(0)
+    B, N, R, nd, H = 2, 4, 2, 5, 8
+    logits = torch.randn(B, N, R, nd * H, generator=g, dtype=torch.float64)
+    probs = torch.softmax(logits, dim=-1).view(B, N, R, nd, H).sum(-1)     # per-row, per-head document mass
+    want = torch.softmax(logits[:, :, -1], dim=-1).view(B, N, nd, H).sum(-1).mean(1)
+    got = notebook_scores(probs)
+    assert got.shape == (B, nd)
+    assert torch.allclose(got, want, atol=1e-12)
+    assert torch.allclose(got.sum(-1), torch.ones(B, dtype=torch.float64))
 
 
 def test_partition_covers_all_prompts():
