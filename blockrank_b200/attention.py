@@ -9,10 +9,10 @@ reference scripts switch to the block collator on that substring,
 scripts/eval_attn.py:36-38).
 
 Differences that matter to callers:
-  * the mask function returns compact block spans, an int32 ``(2, B, M)``
-    tensor (start, length per block), instead of the ``(B,1,M,H,H)`` additive
-    mask of std:264-309; an int32 ``(2, B, M)`` tensor passed as
-    ``attention_mask`` is taken as spans already (padding-free layout);
+  * the mask function returns compact block spans (``BlockSpans``: an int32
+    ``(2, B, M)`` tensor of start and length per block) instead of the
+    ``(B,1,M,H,H)`` additive mask of std:264-309; a ``BlockSpans`` passed as
+    ``attention_mask`` is used as it is (padding-free layout);
   * K/V heads are shared inside the kernel (no ``repeat_kv`` copy) and the
     output is written directly as ``(B, S, N, D)``;
   * forward only: autograd through it raises NotImplementedError, like the
@@ -31,12 +31,17 @@ ATTN_NAME = "cuda_blockrank"
 
 
 class BlockSpans(torch.Tensor):
-    """int32 (2, B, M) tensor [starts; lengths] that also carries ``max_block_len``."""
+    """int32 (2, B, M) tensor [starts; lengths] that also carries ``max_block_len``, ``max_query_len`` (0 if
+    unknown) and ``grid_h`` (the H of the reference's (M, H) grid it was derived from, None for a padding-free
+    layout)."""
 
     @staticmethod
-    def make(start: torch.Tensor, length: torch.Tensor, max_block_len: int) -> "BlockSpans":
+    def make(start: torch.Tensor, length: torch.Tensor, max_block_len: int, grid_h: Optional[int] = None,
+             max_query_len: int = 0) -> "BlockSpans":
         t = torch.stack([start.to(torch.int32), length.to(torch.int32)]).contiguous().as_subclass(BlockSpans)
         t.max_block_len = int(max_block_len)
+        t.max_query_len = int(max_query_len)
+        t.grid_h = grid_h
         return t
 
 
@@ -44,22 +49,19 @@ def cuda_blockrank_attention_mask(*args, attention_mask: Optional[torch.Tensor] 
     """Mask-interface entry.  Accepts both calling conventions of transformers (with or
     without ``cache_position``; everything but ``attention_mask`` is ignored).
 
-    attention_mask: (B, M, H) bool/0-1 block mask from the block collator
-    (src/blockrank/dataset.py:228), or int32 (2, B, M) spans.
+    attention_mask: the (B, M, H) bool/0-1 block mask of the block collator
+    (src/blockrank/dataset.py:228), or a :class:`BlockSpans` (padding-free layout; build one with
+    ``BlockSpans.make(start, length, max_block_len)``).  A plain int32 tensor is always read as a 0/1
+    block mask, whatever its shape.
     """
     if attention_mask is None:
         raise ValueError("cuda_blockrank attention needs the (B, M, H) block attention_mask of the block collator")
     if isinstance(attention_mask, BlockSpans):
         return attention_mask
     if attention_mask.dim() != 3:
-        raise ValueError(f"expected a (B, M, H) block mask or (2, B, M) spans, got shape {tuple(attention_mask.shape)}")
-    if attention_mask.dtype == torch.int32 and attention_mask.shape[0] == 2:
-        mbl = kwargs.get("max_block_len")
-        if mbl is None:
-            mbl = int(attention_mask[1].max().item())
-        return BlockSpans.make(attention_mask[0], attention_mask[1], mbl)
+        raise ValueError(f"expected a (B, M, H) block mask or BlockSpans, got shape {tuple(attention_mask.shape)}")
     start, length = ops.spans_from_mask(attention_mask)
-    return BlockSpans.make(start, length, attention_mask.shape[-1])
+    return BlockSpans.make(start, length, attention_mask.shape[-1], grid_h=attention_mask.shape[-1])
 
 
 def _wants_scores(module, kwargs) -> bool:
@@ -96,7 +98,8 @@ def cuda_blockrank_attention_forward(module, query, key, value, attention_mask, 
     spans = attention_mask
     start, length = spans[0], spans[1]
     out = ops.attention(query, key, value, start, length, scaling, spans.max_block_len,
-                        algo=kwargs.get("blockrank_algo", _lib.ALGO_AUTO))
+                        algo=kwargs.get("blockrank_algo", _lib.ALGO_AUTO),
+                        max_query_len=getattr(spans, "max_query_len", 0))
     scores = None
     if start.shape[-1] > 1 and _wants_scores(module, kwargs):
         if kwargs.get("blockrank_doc_scores", False):
@@ -106,7 +109,8 @@ def cuda_blockrank_attention_forward(module, query, key, value, attention_mask, 
             scores, _ = ops.doc_scores(query, key, start, length, rows.to(device=query.device, dtype=torch.int32),
                                        scaling, kwargs.get("temperature", 0.05))
         else:
-            scores = ops.raw_scores(query, key, start, length, scaling, kwargs.get("num_last_queries", 16))
+            scores = ops.raw_scores(query, key, start, length, scaling, kwargs.get("num_last_queries", 16),
+                                    grid_h=getattr(spans, "grid_h", None))
     return out, scores
 
 

@@ -24,6 +24,7 @@ struct SimtArgs {
   float* lse;
   const int32_t* blk_start;
   const int32_t* blk_len;
+  const int* hdr;  // workspace header: hdr[1] != 0 when the prologue kernel found the block spans malformed
   int B, N, Nk, S, M;
   float scale_log2;  // scale * log2(e)
 };
@@ -35,6 +36,7 @@ __global__ void __launch_bounds__(kThreads) attn_simt_kernel(SimtArgs a) {
   __shared__ __align__(16) float Ks[kKeyTile][D];
   __shared__ __align__(16) float Vs[kKeyTile][D];
 
+  if (a.hdr[1] != 0) return;  // malformed spans: write nothing
   const int tid = threadIdx.x;
   const int b = blockIdx.z / a.Nk, g = blockIdx.z % a.Nk;
   const int m = a.M - 1 - blockIdx.y;  // the long query-block CTAs are scheduled first
@@ -183,8 +185,13 @@ int launch_g(const brk_attn_params& p, const SimtArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-int attn_simt_launch(const brk_attn_params& p, cudaStream_t st) {
+int attn_simt_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
+  BRK_REQUIRE(ws != nullptr && ws_bytes >= kWsHeader && ((uintptr_t)ws & 15) == 0, BRK_E_WORKSPACE,
+              "attention workspace: %zu bytes (16-byte aligned) needed, %zu given", kWsHeader, ws_bytes);
+  int rc = attn_prologue_launch(p, reinterpret_cast<int*>(ws), nullptr, 0, st);
+  if (rc) return rc;
   SimtArgs a;
+  a.hdr = reinterpret_cast<const int*>(ws);
   a.q = make_view(p.q);
   a.k = make_view(p.k);
   a.v = make_view(p.v);

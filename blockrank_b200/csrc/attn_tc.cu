@@ -1,34 +1,39 @@
 // BlockRank attention forward on the sm_100a tensor cores (tcgen05 + TMEM), fed by TMA.
 //
-// Persistent, warp-specialised kernel: one CTA per SM; the CTAs claim work items (longest first)
-// from a global counter.  A work item is (prompt b, KV head g, block m, pair of row tiles[, key chunk]); a row tile is
-// 128 MMA rows = 128/G consecutive query tokens x the G query heads that share KV head g, so
-// one K/V tile in shared memory serves the whole GQA group and a Q tile is one 3-D TMA box of
-// the [B,S,N,D] tensor.  The two row tiles of a pair ("chains") share the item's K/V tiles and
-// are processed in ping-pong: while one chain's 128 softmax threads work on their S tile, the
-// tensor core runs the other chain's MMAs.
+// Persistent, warp-specialised kernel: one CTA per SM; the CTAs claim work items from a global
+// counter.  Two independent "chains" run in every CTA.  A chain owns one 128-row tile at a time
+// (128/G consecutive query tokens x the G query heads that share a KV head, so one K/V tile
+// serves the whole GQA group and a Q tile is one 3-D TMA box of the [B,S,N,D] tensor), a
+// 256-column half of tensor memory (S 128 columns, O 128 columns), a Q buffer, four softmax
+// warps and its own MMA-issuing warp.  Chains are fed with "jobs" (one row tile against a list
+// of 64-key slots) through per-chain record rings and never wait for one another, so one
+// chain's MMAs run while the other chain's softmax threads work.
 //
-// Only live keys are visited, in 64-key slots (one TMA box each):
+// Only live keys are visited:
 //   block 0            : own keys, causal
 //   document block     : the prefix block's keys, then own keys, causal
-//   query (last) block : every slot of the earlier blocks, then own keys, causal; its context
-//                        is cut into key chunks, each a work item that leaves an un-normalised
-//                        partial (O, max, sum); attn_combine_kernel merges them.
-// Two consecutive slots form one 128-key MMA tile (a document's prefix slot and its first own
-// slot share a tile), which halves the barrier hops per key and runs QK^T at the full N=128 rate.
+//   query (last) block : every slot of the earlier blocks, then own keys, causal
 //
-// Roles (320 threads):
+// Two kinds of work item:
+//   * resident block  (blocks 0 .. M-2 whose prefix + own keys fit the five 64-key slots of
+//     shared memory): the block's K/V is loaded ONCE, its row tiles are dealt to the two chains
+//     largest first, and every slot is handed back as soon as the remaining (smaller) row tiles
+//     of both chains no longer need it, so the next block's loads overlap the tail of this one.
+//   * streamed pair   (the query block, cut into chunks of about 1024 context keys that leave
+//     un-normalised partials (O, max, sum) merged by attn_combine_kernel; also any block too
+//     long to be resident): the two chains take the two row tiles of a pair and walk the same
+//     128-key tiles through a two-deep ring.
+//
+// Roles (352 threads):
 //   warps 0-3 / 4-7  softmax + output of chain 0 / 1 (thread = row = TMEM lane)
-//   warp 8           TMA producer: claims and decodes the items (the decoded item goes to the other
-//                    roles through a 4-deep record ring in shared memory), loads Q tiles and a
-//                    2-stage ring of 128-key K/V tiles, running ahead across items
-//   warp 9           MMA issuer: S = Q K^T (both operands K-major, 128B swizzle) and O += P V
-//                    (P read from tensor memory, V as the MN-major B operand)
-// O stays in TMEM across the key tiles of an item; softmax is base-2, online, with a lazy
-// rescale (O is only touched when the running max grows by more than 2^8).  P (bf16, two keys
-// per 32-bit column) overwrites the first half of the S tile it was computed from.
+//   warp 8           TMA producer: claims and decodes items, publishes jobs, loads Q and K/V
+//   warps 9 / 10     MMA issuer of chain 0 / 1: S = Q K^T (both operands K-major, 128B swizzle)
+//                    and O += P V (P read from tensor memory, V as the MN-major B operand)
+// Softmax is base-2, online, with a lazy rescale (O is only touched when the running max grows
+// by more than 2^8).  P (bf16, two keys per 32-bit column) overwrites the first half of the S
+// tile it was computed from.
 //
-// Shared memory 194 KB: Q 2x32 KB, K/V ring 2x64 KB, barriers, item records.  TMEM: 2 x (S 128 + O 128) columns.
+// Shared memory 226 KB: Q 2x32 KB, K pool 80 KB, V pool 80 KB, barriers, job records.
 // No cluster multicast anywhere.  Every mbarrier wait is bounded; on expiry the thread records
 // a code in the caller's status word, stops waiting and runs to the normal exit.
 #include <cuda.h>
@@ -71,26 +76,27 @@ int make_tmap_bf16(CUtensorMap* out, const void* ptr, int D, int heads, int S, i
   return BRK_OK;
 }
 
-
-
 namespace {
 
 constexpr int BM = 128;  // query rows (token, head) per row tile
 constexpr int BN = 64;   // keys per slot (one TMA box)
 constexpr int BT = 128;  // keys per MMA tile (two slots)
 constexpr int HD = 128;  // head dim
-constexpr int kStages = 2;
-constexpr int kThreads = 320;
-constexpr uint32_t kQBytes = 2 * BM * 128;  // two 64-wide halves of D
-constexpr uint32_t kSlotBytes = 2 * BN * 128;  // K (or V) of one 64-key slot
-constexpr uint32_t kKBytes = 2 * BT * 128;     // one K (or V) tile: [d half][128 keys][128 B]
-constexpr uint32_t kStageBytes = 2 * kKBytes;
+constexpr int kSlots = 5;        // 64-key K/V slots in shared memory
+constexpr int kGroup = 4;        // consecutive blocks of one (prompt, KV head) per work item
+constexpr int kThreads = 352;
+constexpr uint32_t kQBytes = 2 * BM * 128;       // one Q tile: two 64-wide halves of D
+constexpr uint32_t kSlotHalf = BN * 128;         // K (or V) of one slot, one 64-wide half of D
+constexpr uint32_t kPoolHalf = kSlots * kSlotHalf;  // all slots of one half of D, contiguous: key k at k * 128 B
+constexpr uint32_t kSlotBytes = 4 * kSlotHalf;   // K + V of one slot
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffKV = kOffQ + 2 * kQBytes;
-constexpr uint32_t kOffBar = kOffKV + kStages * kStageBytes;
-constexpr int kItemRing = 4;                        // decoded work items in flight between the producer and its consumers
-constexpr uint32_t kOffItems = kOffBar + 256;       // kItemRing records of 16 ints
-constexpr uint32_t kSmemBytes = kOffItems + kItemRing * 64 + 1024;  // + slack for the 1024-byte round-up
+constexpr uint32_t kOffK = kOffQ + 2 * kQBytes;
+constexpr uint32_t kOffV = kOffK + 2 * kPoolHalf;
+constexpr uint32_t kOffBar = kOffV + 2 * kPoolHalf;
+constexpr int kJobRing = 4;                      // published jobs in flight per chain
+constexpr uint32_t kOffJobs = kOffBar + 512;     // 2 x kJobRing records of 16 ints
+constexpr uint32_t kSmemBytes = kOffJobs + 2 * kJobRing * 64 + 1024;  // + slack for the 1024-byte round-up
+static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kChainCols = 256;  // per chain: S [0,128) (P over its first 64 columns), then O [128,256)
 constexpr uint32_t kColO = 128;
@@ -99,18 +105,18 @@ constexpr uint32_t kWaitBudget = 1u << 18;
 
 enum {
   kQFull = 0,    // +chain  TMA -> MMA: Q tile landed
-  kQFree = 2,    // +chain  MMA -> TMA: every QK^T of the item has read Q
-  kSFull = 4,    // +chain  MMA -> softmax: S tile complete (+2, +3 unused)
-  kPFull = 8,    // +chain  softmax -> MMA: P written to tensor memory, S consumed (4 warp arrivals)
-  kPVDone = 10,  // +chain  MMA -> softmax: P V of a tile complete
-  kOFree = 12,   // +chain  softmax -> MMA: O read out of TMEM (4 warp arrivals)
-  kKVFull = 14,  // +stage  TMA -> MMA
-  kKVFree = 14 + kStages,  // +stage  MMA -> TMA
-  kItemFull = 14 + 2 * kStages,           // +ring slot  TMA warp -> MMA, softmax: item record written
-  kItemFree = kItemFull + kItemRing,      // +ring slot  MMA + 8 softmax warps -> TMA warp: record copied (9 arrivals)
-  kNumBars = kItemFree + kItemRing
+  kQFree = 2,    // +chain  MMA -> TMA: every QK^T of the job has read Q
+  kSFull = 4,    // +chain  MMA -> softmax: S tile complete
+  kPFull = 6,    // +chain  softmax -> MMA: P written to tensor memory, S consumed (4 warp arrivals)
+  kPVDone = 8,   // +chain  MMA -> softmax: P V of a tile complete
+  kOFree = 10,   // +chain  softmax -> MMA: O read out of TMEM (4 warp arrivals)
+  kKVFull = 12,              // +slot  TMA -> MMA warps: K and V of the slot (or of the tile that starts there) landed
+  kKVFree = kKVFull + kSlots,  // +slot  both MMA warps -> TMA: no MMA still reads the slot (2 arrivals)
+  kJobFull = kKVFree + kSlots,            // +chain*kJobRing+i  TMA warp -> MMA warp, softmax warps: record written
+  kJobFree = kJobFull + 2 * kJobRing,     // +chain*kJobRing+i  MMA warp + 4 softmax warps -> TMA warp (5 arrivals)
+  kNumBars = kJobFree + 2 * kJobRing
 };
-static_assert(kNumBars * 8 + 4 <= 256, "barrier area");
+static_assert(kNumBars * 8 + 4 <= 512, "barrier area");
 
 // Division by a run-time constant with a host-computed reciprocal (round-up method, exact for every
 // 32-bit numerator): q = umulhi(n, mul); n / d = (((n - q) >> 1) + q) >> shift.
@@ -139,127 +145,39 @@ struct TcArgs {
   const int32_t* blk_start;
   const int32_t* blk_len;
   int32_t* status;
+  const int* hdr;   // workspace header: [0] work counter, [1] non-zero if the block spans are malformed
   int B, N, Nk, S, M;
   int G, g_shift;   // query heads per KV head, log2
   float scale_log2;
   int n_split;      // key chunks of the query block's context (1 = no split)
-  int lq_max;       // rows per (prompt, head) in the partial buffers (= max_block_len)
-  int pairs;        // row-tile pairs per block (covers max_block_len)
+  int lq_max;       // rows per (prompt, head) in the partial buffers (bound on the query block's length)
+  int pairs_q;      // row-tile pairs of the query block (covers lq_max)
+  int n_groups;     // groups of kGroup blocks among blocks 0 .. M-2
   int o_align32;    // output rows are 32-byte aligned (enables 32-byte stores)
-  int total_items;
-  FastDiv div_sec1, div_nbg, div_sec2, div_nk;  // by nbg*n_split, nbg, nbg*(M-1), Nk
+  int sec1, total_items;
+  FastDiv div_sec1, div_nbg, div_nk;  // by nbg*n_split, nbg, Nk
   int* work_counter;  // next unclaimed index of the work list (zeroed before the launch)
   float* part_o;    // [B, N, lq_max, n_split, 128] un-normalised partial outputs
   float2* part_ml;  // [B, N, lq_max, n_split] (running max in log2 units, sum)
 };
 
-struct Item {
+// One row tile against a list of 64-key slots: what a chain works on.
+constexpr int kFSplit = 1, kFCtxCheck = 2, kFStop = 4, kFDoc = 8, kFFirst = 16, kFKeep = 32;
+struct Job {
   int b, g, m, chunk;
   int start, len;        // span of block m
-  int t0_0, t0_1;        // first token of each chain's row tile
-  int n_0, n_1;          // key tiles visible to each chain (a prefix of the item's tile list)
-  // selected with a conditional move rather than an indexed array, so the item stays in registers
-  __device__ __forceinline__ int t0(int x) const { return x ? t0_1 : t0_0; }
-  __device__ __forceinline__ int n_x(int x) const { return x ? n_1 : n_0; }
-  int ctx_lo, ctx_hi;    // context key range (slots)
-  int n_ctx, j0;         // context tiles of the block, first tile of this item
-  int n_tiles, own_n;
-  bool split, valid;
+  int t0;                // first token of the row tile
+  int n;                 // key slots visible to this row tile (0: nothing to compute, only slots to hand back)
+  int ctx_lo, ctx_hi;    // context key range (token slots of the prompt)
+  int n_ctx, j0;         // context slots of the block, first slot of this job's list
+  int own_n;             // own keys covered by the slot list
+  int flags;
+  int tile0;             // streamed: ring position (0/1) of the job's first 128-key tile
+  int aux;               // streamed: tiles of the item; resident: rel_lo | rel_hi << 8 (slots handed back after the job)
 };
 
-// Block spans an item needs, fetched one item ahead of their use: decoding is two dependent
-// global-memory round trips, which would otherwise sit on every role's critical path.
-struct ItemRaw {
-  int m, chunk, p, b, g;
-  int start, len;      // span of block m
-  int s0, l0;          // span of block 0 (the prefix)
-  int s2, l2;          // span of block M-2 (end of the query block's context)
-};
-
-// Work list order: query-block chunks first (longest), then blocks M-2 .. 0.
-__device__ __forceinline__ ItemRaw load_item(const TcArgs& a, int idx) {
-  ItemRaw r;
-  if (idx >= a.total_items) idx = a.total_items - 1;  // prefetch past the end: harmless reload
-  const int nbg = a.B * a.Nk;
-  const int sec1 = nbg * a.n_split * a.pairs;
-  int bg;
-  if (idx < sec1) {
-    r.p = (int)fdiv((uint32_t)idx, a.div_sec1);
-    const int q = idx - r.p * (nbg * a.n_split);
-    r.chunk = (int)fdiv((uint32_t)q, a.div_nbg);
-    bg = q - r.chunk * nbg;
-    r.m = a.M - 1;
-  } else {
-    const int i2 = idx - sec1;
-    r.p = (int)fdiv((uint32_t)i2, a.div_sec2);
-    const int q = i2 - r.p * (nbg * (a.M - 1));
-    const int mm = (int)fdiv((uint32_t)q, a.div_nbg);
-    r.m = a.M - 2 - mm;
-    bg = q - mm * nbg;
-    r.chunk = 0;
-  }
-  r.b = (int)fdiv((uint32_t)bg, a.div_nk);
-  r.g = bg - r.b * a.Nk;
-  const int32_t* bs = a.blk_start + (size_t)r.b * a.M;
-  const int32_t* bl = a.blk_len + (size_t)r.b * a.M;
-  const int m2 = a.M >= 2 ? a.M - 2 : 0;
-  r.start = bs[r.m];
-  r.len = bl[r.m];
-  r.s0 = bs[0];
-  r.l0 = bl[0];
-  r.s2 = bs[m2];
-  r.l2 = bl[m2];
-  return r;
-}
-
-__device__ __forceinline__ Item decode_item(const TcArgs& a, const ItemRaw& r) {
-  Item it;
-  const int TOK = BM >> a.g_shift;
-  it.b = r.b; it.g = r.g; it.m = r.m; it.chunk = r.chunk;
-  it.start = r.start;
-  it.len = r.len;
-  it.t0_0 = 2 * r.p * TOK;
-  it.t0_1 = it.t0_0 + TOK;
-  it.valid = it.t0_0 < it.len;
-  it.split = it.m == a.M - 1 && a.n_split > 1;
-  it.ctx_lo = it.ctx_hi = 0;
-  it.n_ctx = it.j0 = it.n_tiles = it.own_n = 0;
-  it.n_0 = it.n_1 = 0;
-  if (!it.valid) return it;
-  if (it.m > 0) {
-    it.ctx_lo = r.s0;
-    it.ctx_hi = (it.m < a.M - 1) ? r.s0 + r.l0 : r.s2 + r.l2;
-  }
-  const bool on1 = it.t0_1 < it.len;
-  it.own_n = min(it.len, (on1 ? it.t0_1 : it.t0_0) + TOK);
-  it.n_ctx = (it.ctx_hi - it.ctx_lo + BN - 1) / BN;
-  const int own_tiles = (it.own_n + BN - 1) / BN;
-  int j1 = it.n_ctx + own_tiles;
-  if (it.split) {
-    const int per = (it.n_ctx + a.n_split - 1) / a.n_split;
-    it.j0 = min(it.n_ctx, it.chunk * per);
-    if (it.chunk != a.n_split - 1) j1 = min(it.n_ctx, it.j0 + per);
-  }
-  it.n_tiles = j1 - it.j0;
-  if (it.n_tiles <= 0) {  // a chunk without tiles: nothing to do (its partial stays neutral)
-    it.valid = false;
-    it.n_tiles = 0;
-    return it;
-  }
-  // own tiles visible to chain x: those starting at or before its last token
-  {
-    const int own_x = min(own_tiles, (min(it.len, it.t0_0 + TOK) + BN - 1) / BN);
-    it.n_0 = max(0, min(j1, it.n_ctx + own_x) - it.j0);
-  }
-  if (on1) {
-    const int own_x = min(own_tiles, (min(it.len, it.t0_1 + TOK) + BN - 1) / BN);
-    it.n_1 = max(0, min(j1, it.n_ctx + own_x) - it.j0);
-  }
-  return it;
-}
-
-// tile j of the item -> first key slot, number of keys, whether it lies in the item's own block
-__device__ __forceinline__ int tile_lo(const Item& it, int j, int& nk, bool& own, int& own_off) {
+// slot j of the job's list -> first key (token slot of the prompt), number of keys, whether it lies in the own block
+__device__ __forceinline__ int tile_lo(const Job& it, int j, int& nk, bool& own, int& own_off) {
   const int jg = j + it.j0;
   own = jg >= it.n_ctx;
   if (!own) {
@@ -273,28 +191,20 @@ __device__ __forceinline__ int tile_lo(const Item& it, int j, int& nk, bool& own
   return it.start + own_off;
 }
 
-// Work items are decoded once, by the TMA warp, and handed to the MMA warp and the softmax warps as
-// 16-int records in shared memory: decoding costs two global-memory round trips and a few hundred
-// scalar instructions, which would otherwise sit on every role's critical path between two items.
-constexpr int kRecSplit = 1, kRecCtxCheck = 2, kRecStop = 4;
-__device__ __forceinline__ void write_record(int* rec, const Item& it, int flags) {
+__device__ __forceinline__ void write_record(int* rec, const Job& it) {
   reinterpret_cast<int4*>(rec)[0] = make_int4(it.b, it.g, it.m, it.chunk);
-  reinterpret_cast<int4*>(rec)[1] = make_int4(it.start, it.len, it.t0_0, it.n_0);
-  reinterpret_cast<int4*>(rec)[2] = make_int4(it.n_1, it.ctx_lo, it.ctx_hi, it.n_ctx);
-  reinterpret_cast<int4*>(rec)[3] = make_int4(it.j0, it.n_tiles, it.own_n, flags);
+  reinterpret_cast<int4*>(rec)[1] = make_int4(it.start, it.len, it.t0, it.n);
+  reinterpret_cast<int4*>(rec)[2] = make_int4(it.ctx_lo, it.ctx_hi, it.n_ctx, it.j0);
+  reinterpret_cast<int4*>(rec)[3] = make_int4(it.own_n, it.flags, it.tile0, it.aux);
 }
-__device__ __forceinline__ Item read_record(const int* rec, int tok_per_tile, int& flags) {
+__device__ __forceinline__ Job read_record(const int* rec) {
   const int4 r0 = reinterpret_cast<const int4*>(rec)[0], r1 = reinterpret_cast<const int4*>(rec)[1];
   const int4 r2 = reinterpret_cast<const int4*>(rec)[2], r3 = reinterpret_cast<const int4*>(rec)[3];
-  Item it;
+  Job it;
   it.b = r0.x; it.g = r0.y; it.m = r0.z; it.chunk = r0.w;
-  it.start = r1.x; it.len = r1.y; it.t0_0 = r1.z; it.n_0 = r1.w;
-  it.t0_1 = it.t0_0 + tok_per_tile;
-  it.n_1 = r2.x; it.ctx_lo = r2.y; it.ctx_hi = r2.z; it.n_ctx = r2.w;
-  it.j0 = r3.x; it.n_tiles = r3.y; it.own_n = r3.z;
-  flags = r3.w;
-  it.split = (flags & kRecSplit) != 0;
-  it.valid = true;
+  it.start = r1.x; it.len = r1.y; it.t0 = r1.z; it.n = r1.w;
+  it.ctx_lo = r2.x; it.ctx_hi = r2.y; it.n_ctx = r2.z; it.j0 = r2.w;
+  it.own_n = r3.x; it.flags = r3.y; it.tile0 = r3.z; it.aux = r3.w;
   return it;
 }
 
@@ -309,10 +219,123 @@ __device__ __forceinline__ bool slot_valid(const int32_t* bs, const int32_t* bl,
   return m >= 0 && s < bs[m] + bl[m];
 }
 
+// A claimed work item before decoding: the spans it needs are fetched one item ahead of their use.
+//   kind 0: streamed pair p, key chunk `chunk`, of the query block (m = M-1)
+//   kind 1: blocks [m, m + cnt) of (b, g); lane i of the warp holds the span of block m + i
+struct ItemRaw {
+  int kind, p, chunk, b, g, m, cnt;
+  int start, len;      // span of block m + lane (kind 1) or of the query block (kind 0)
+  int s0, l0;          // span of block 0 (the prefix)
+  int s2, l2;          // span of block M-2 (end of the query block's context)
+};
+
+// Work list: streamed pairs of the query block first (the longest items), then the groups of blocks 0 .. M-2.
+__device__ __forceinline__ ItemRaw load_item(const TcArgs& a, int idx, int lane) {
+  ItemRaw r;
+  if (idx >= a.total_items) idx = a.total_items - 1;  // prefetch past the end: harmless reload
+  const int nbg = a.B * a.Nk;
+  int bg;
+  if (idx < a.sec1) {
+    r.kind = 0;
+    r.p = (int)fdiv((uint32_t)idx, a.div_sec1);
+    const int q = idx - r.p * (nbg * a.n_split);
+    r.chunk = (int)fdiv((uint32_t)q, a.div_nbg);
+    bg = q - r.chunk * nbg;
+    r.m = a.M - 1;
+    r.cnt = 1;
+  } else {
+    r.kind = 1;
+    const int i2 = idx - a.sec1;
+    const int grp = (int)fdiv((uint32_t)i2, a.div_nbg);
+    bg = i2 - grp * nbg;
+    r.m = grp * kGroup;
+    r.cnt = min(kGroup, a.M - 1 - r.m);
+    r.p = r.chunk = 0;
+  }
+  r.b = (int)fdiv((uint32_t)bg, a.div_nk);
+  r.g = bg - r.b * a.Nk;
+  const int32_t* bs = a.blk_start + (size_t)r.b * a.M;
+  const int32_t* bl = a.blk_len + (size_t)r.b * a.M;
+  const int m2 = a.M >= 2 ? a.M - 2 : 0;
+  const int mm = min(r.m + (r.kind ? lane : 0), a.M - 1);
+  r.start = bs[mm];
+  r.len = bl[mm];
+  r.s0 = bs[0];
+  r.l0 = bl[0];
+  r.s2 = bs[m2];
+  r.l2 = bl[m2];
+  return r;
+}
+
+// A streamed pair: the two row tiles [2p, 2p+1] of block m against the block's slot list (or one key chunk of it).
+struct Pair {
+  Job job;         // fields common to both chains
+  int t0_0, t0_1;  // first token of each chain's row tile
+  int n_0, n_1;    // slots visible to each chain (a prefix of the item's slot list)
+  int n_slots;     // slots of the item
+  bool valid;
+};
+
+__device__ __forceinline__ Pair decode_pair(const TcArgs& a, int b, int g, int m, int chunk, int p, int start, int len,
+                                            int s0, int l0, int s2, int l2) {
+  Pair pr;
+  Job& it = pr.job;
+  const int TOK = BM >> a.g_shift;
+  it.b = b; it.g = g; it.m = m; it.chunk = chunk;
+  it.start = start;
+  it.len = len;
+  pr.t0_0 = 2 * p * TOK;
+  pr.t0_1 = pr.t0_0 + TOK;
+  pr.valid = pr.t0_0 < len;
+  const bool split = m == a.M - 1 && a.n_split > 1;
+  it.flags = split ? kFSplit : 0;
+  it.ctx_lo = it.ctx_hi = 0;
+  it.n_ctx = it.j0 = it.own_n = 0;
+  it.t0 = it.n = it.tile0 = it.aux = 0;
+  pr.n_0 = pr.n_1 = pr.n_slots = 0;
+  if (!pr.valid) return pr;
+  if (m > 0) {
+    it.ctx_lo = s0;
+    it.ctx_hi = (m < a.M - 1) ? s0 + l0 : s2 + l2;
+  }
+  const bool on1 = pr.t0_1 < len;
+  it.own_n = min(len, (on1 ? pr.t0_1 : pr.t0_0) + TOK);
+  it.n_ctx = (it.ctx_hi - it.ctx_lo + BN - 1) / BN;
+  const int own_slots = (it.own_n + BN - 1) / BN;
+  int j1 = it.n_ctx + own_slots;
+  if (split) {
+    const int per = (it.n_ctx + a.n_split - 1) / a.n_split;
+    it.j0 = min(it.n_ctx, chunk * per);
+    if (chunk != a.n_split - 1) j1 = min(it.n_ctx, it.j0 + per);
+  }
+  pr.n_slots = j1 - it.j0;
+  if (pr.n_slots <= 0) {  // a chunk without slots: nothing to do (its partial stays neutral)
+    pr.valid = false;
+    pr.n_slots = 0;
+    return pr;
+  }
+  // own slots visible to chain x: those starting at or before its last token
+  {
+    const int own_x = min(own_slots, (min(len, pr.t0_0 + TOK) + BN - 1) / BN);
+    pr.n_0 = max(0, min(j1, it.n_ctx + own_x) - it.j0);
+  }
+  if (on1) {
+    const int own_x = min(own_slots, (min(len, pr.t0_1 + TOK) + BN - 1) / BN);
+    pr.n_1 = max(0, min(j1, it.n_ctx + own_x) - it.j0);
+  }
+  return pr;
+}
+
+// chain of the i-th largest row tile of a resident block (tiles are dealt 0,1,1,0,0,1,1,0,...) and the
+// position of the same chain's next tile
+__device__ __forceinline__ int deal_chain(int i) { return ((i & 3) == 0 || (i & 3) == 3) ? 0 : 1; }
+__device__ __forceinline__ int deal_next(int i) { return ((i & 3) == 0 || (i & 3) == 2) ? i + 3 : i + 1; }
+
 __global__ void __launch_bounds__(kThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (a.hdr[1] != 0) return;  // malformed block spans (found by the prologue kernel): write nothing
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = a.G;
 
@@ -343,9 +366,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   bool failed = false;
   if (tid == 0) {
     for (int i = 0; i < kNumBars; ++i) {
-      const bool many = (i >= kPFull && i < kPFull + 2) || (i >= kOFree && i < kOFree + 2);
-      const bool rec_free = i >= kItemFree && i < kItemFree + kItemRing;
-      ptx::mbar_init(bar(i), rec_free ? 9u : many ? 4u : 1u);  // one arrival per softmax warp (+ the MMA warp)
+      uint32_t cnt = 1u;
+      if ((i >= kPFull && i < kPFull + 2) || (i >= kOFree && i < kOFree + 2)) cnt = 4u;  // one arrival per softmax warp
+      if (i >= kKVFree && i < kKVFree + kSlots) cnt = 2u;                                 // one per MMA warp
+      if (i >= kJobFree) cnt = 5u;                                                        // MMA warp + four softmax warps
+      ptx::mbar_init(bar(i), cnt);
     }
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmQ);
@@ -370,16 +395,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   };
 
-  int* const item_ring = reinterpret_cast<int*>(smem + kOffItems);
+  int* const job_ring = reinterpret_cast<int*>(smem + kOffJobs);
   const int TOK = BM >> a.g_shift;
-  // consumer side of the item ring: copy record number i, release its slot
-  auto next_item = [&](uint32_t i, int& flags) {
-    const uint32_t slot = i % kItemRing;
-    wait(kItemFull + slot, i / kItemRing, 40);
-    Item it = read_record(item_ring + slot * 16, TOK, flags);
-    if (__any_sync(0xffffffffu, failed)) flags |= kRecStop;  // a wait gave up: the whole warp stops here
+  // consumer side of chain x's job ring: copy record number i, release its slot
+  auto next_job = [&](int x, uint32_t i) {
+    const uint32_t slot = i % kJobRing;
+    wait(kJobFull + x * kJobRing + slot, i / kJobRing, 40 + x);
+    Job it = read_record(job_ring + (x * kJobRing + slot) * 16);
+    if (__any_sync(0xffffffffu, failed)) it.flags |= kFStop;  // a wait gave up: the whole warp stops here
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(bar(kItemFree + slot));
+    if (lane == 0) ptx::mbar_arrive(bar(kJobFree + x * kJobRing + slot));
     return it;
   };
 
@@ -387,180 +412,314 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // =============================== TMA producer ===============================================
     // The whole warp runs the control flow (so addresses and counters stay warp-uniform); one lane
     // issues the copies.
-    {
-      const bool leader = lane == 0;
-      uint32_t kv_cnt = 0, q_loads[2] = {0, 0}, n_pub = 0;
-      // record number n_pub -> ring; its slot must have been copied by all nine consumers
-      auto publish = [&](const Item& it, int flags) {
-        const uint32_t slot = n_pub % kItemRing;
-        if (n_pub >= kItemRing) wait(kItemFree + slot, n_pub / kItemRing - 1, 14);
-        if (leader) {
-          write_record(item_ring + slot * 16, it, flags);
-          ptx::mbar_arrive(bar(kItemFull + slot));  // release: the record is visible to whoever sees the phase flip
-        }
-        ++n_pub;
-      };
-      // The work list (longest items first) is handed out dynamically: whichever CTA is free claims
-      // the next index.  Claims run two items ahead and the block spans of a claimed item one item
-      // ahead, so neither the atomic nor the loads are waited for.
-      auto claim = [&]() {
-        int v = 0;
-        if (leader) v = atomicAdd(a.work_counter, 1);
-        return __shfl_sync(0xffffffffu, v, 0);
-      };
-      int idx = claim(), idx_next = claim();
-      ItemRaw raw_next = load_item(a, idx);
-      Item it{};
-      for (; idx < a.total_items; idx = idx_next, idx_next = claim()) {
-        const ItemRaw raw = raw_next;
-        raw_next = load_item(a, idx_next);  // in flight while this item is processed
-        it = decode_item(a, raw);
-        if (!it.valid) continue;
-        int flags = it.split ? kRecSplit : 0;
-        if (it.m == a.M - 1 && it.m > 0) {  // the query block's context may contain padding slots
-          const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
-          int part = 0;
-          for (int i = lane; i < a.M - 1; i += 32) part += bl[i];
+    const bool leader = lane == 0;
+    uint32_t n_pub[2] = {0, 0}, q_loads[2] = {0, 0};
+    uint32_t out_mask = 0;    // bit s: a load signalled on barrier kKVFull+s has not been handed back yet
+    uint32_t free_par = 0;    // bit s: parity of the next kKVFree+s phase
+    uint32_t stream_tiles = 0;
+    int mode = 0;             // 1 streamed, 2 resident: the two use the slots' barriers differently
+    auto publish = [&](int x, const Job& it) {
+      const uint32_t slot = n_pub[x] % kJobRing;
+      if (n_pub[x] >= kJobRing) wait(kJobFree + x * kJobRing + slot, n_pub[x] / kJobRing - 1, 14 + x);
+      if (leader) {
+        write_record(job_ring + (x * kJobRing + slot) * 16, it);
+        ptx::mbar_arrive(bar(kJobFull + x * kJobRing + slot));  // release: the record is visible to whoever sees the phase flip
+      }
+      ++n_pub[x];
+    };
+    // wait until both MMA warps have handed back the load last signalled on barrier s
+    auto drain = [&](int s) {
+      if ((out_mask >> s) & 1u) {
+        wait(kKVFree + s, (free_par >> s) & 1u, 12);
+        free_par ^= 1u << s;
+        out_mask &= ~(1u << s);
+      }
+    };
+    auto set_mode = [&](int m) {
+      if (mode != m) {
 #pragma unroll
-          for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-          if (part != (it.ctx_hi - it.ctx_lo)) flags |= kRecCtxCheck;
-        }
-        publish(it, flags);
-        for (int x = 0; x < 2; ++x) {
-          if (it.n_x(x) == 0) continue;
-          if (q_loads[x] > 0) wait(kQFree + x, q_loads[x] - 1, 10 + x);
-          const uint32_t dst = sbase + kOffQ + (uint32_t)x * kQBytes;
-          if (leader) {
-            ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
-            ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, it.g * G, it.start + it.t0(x), it.b);
-            ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, it.g * G, it.start + it.t0(x), it.b);
+        for (int s = 0; s < kSlots; ++s) drain(s);
+        mode = m;
+      }
+    };
+    auto load_q = [&](int x, int g, int b, int tok) {
+      if (q_loads[x] > 0) wait(kQFree + x, q_loads[x] - 1, 10 + x);
+      const uint32_t dst = sbase + kOffQ + (uint32_t)x * kQBytes;
+      if (leader) {
+        ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
+        ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, g * G, tok, b);
+        ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, g * G, tok, b);
+      }
+      ++q_loads[x];
+    };
+    // K and V of 64 keys starting at token slot `lo` -> pool slot s, completion on barrier `bs`
+    auto load_slot = [&](int s, int bs, int g, int b, int lo) {
+      const uint32_t kd = sbase + kOffK + (uint32_t)s * kSlotHalf, vd = sbase + kOffV + (uint32_t)s * kSlotHalf;
+      ptx::tma_load_4d(kd, &tmK, bar(kKVFull + bs), 0, g, lo, b);
+      ptx::tma_load_4d(kd + kPoolHalf, &tmK, bar(kKVFull + bs), 64, g, lo, b);
+      ptx::tma_load_4d(vd, &tmV, bar(kKVFull + bs), 0, g, lo, b);
+      ptx::tma_load_4d(vd + kPoolHalf, &tmV, bar(kKVFull + bs), 64, g, lo, b);
+    };
+
+    // ---- streamed pair: both chains walk the same 128-key tiles through a two-deep ring (slots 0-1, 2-3) ----
+    auto run_pair = [&](int b, int g, int m, int chunk, int p, int start, int len, int s0, int l0, int s2, int l2) {
+      Pair pr = decode_pair(a, b, g, m, chunk, p, start, len, s0, l0, s2, l2);
+      if (!pr.valid) return;
+      Job& it = pr.job;
+      if (m == a.M - 1 && m > 0) {  // the query block's context may contain padding slots
+        const int32_t* bl = a.blk_len + (size_t)b * a.M;
+        int part = 0;
+        for (int i = lane; i < a.M - 1; i += 32) part += bl[i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+        if (part != (it.ctx_hi - it.ctx_lo)) it.flags |= kFCtxCheck;
+      }
+      set_mode(1);
+      const int T = (pr.n_slots + 1) >> 1;
+      it.tile0 = (int)(stream_tiles & 1u);
+      it.aux = T;
+      it.t0 = pr.t0_0; it.n = pr.n_0;
+      publish(0, it);
+      it.t0 = pr.t0_1; it.n = pr.n_1;
+      publish(1, it);
+      if (pr.n_0 > 0) load_q(0, g, b, start + pr.t0_0);
+      if (pr.n_1 > 0) load_q(1, g, b, start + pr.t0_1);
+      for (int t = 0; t < T; ++t) {
+        const int tb = (int)((stream_tiles + (uint32_t)t) & 1u);
+        drain(2 * tb);
+        drain(2 * tb + 1);
+        const int nslots = min(2, pr.n_slots - 2 * t);
+        if (leader) {
+          ptx::mbar_expect_tx(bar(kKVFull + 2 * tb), (uint32_t)nslots * kSlotBytes);
+          for (int h = 0; h < nslots; ++h) {
+            int nk, own_off; bool own;
+            const int lo = tile_lo(it, 2 * t + h, nk, own, own_off);
+            load_slot(2 * tb + h, 2 * tb, g, b, lo);
           }
-          ++q_loads[x];
         }
-        for (int t = 0; 2 * t < it.n_tiles; ++t) {
-          const uint32_t st = kv_cnt % kStages, use = kv_cnt / kStages;
-          if (use > 0) wait(kKVFree + st, use - 1, 12);
-          const uint32_t dst = sbase + kOffKV + st * kStageBytes;
-          const int nslots = min(2, it.n_tiles - 2 * t);
-          if (leader) {
-            ptx::mbar_expect_tx(bar(kKVFull + st), (uint32_t)nslots * 2 * kSlotBytes);
-            for (int h = 0; h < nslots; ++h) {
-              int nk, own_off; bool own;
-              const int lo = tile_lo(it, 2 * t + h, nk, own, own_off);
-              const uint32_t row = dst + (uint32_t)h * (BN * 128);  // slot h = key rows [64h, 64h+64) of the tile
-              ptx::tma_load_4d(row, &tmK, bar(kKVFull + st), 0, it.g, lo, it.b);
-              ptx::tma_load_4d(row + BT * 128, &tmK, bar(kKVFull + st), 64, it.g, lo, it.b);
-              ptx::tma_load_4d(row + kKBytes, &tmV, bar(kKVFull + st), 0, it.g, lo, it.b);
-              ptx::tma_load_4d(row + kKBytes + BT * 128, &tmV, bar(kKVFull + st), 64, it.g, lo, it.b);
-            }
-          }
-          ++kv_cnt;
+        out_mask |= 1u << (2 * tb);
+      }
+      stream_tiles += (uint32_t)T;
+    };
+
+    // ---- resident block: K/V loaded once, row tiles dealt to the chains largest first ----
+    auto run_block = [&](int b, int g, int m, int start, int len, int s0, int l0, bool keep_in, bool keep_out) {
+      const int ctx = m > 0 ? l0 : 0;
+      const int n_ctx = (ctx + BN - 1) / BN;
+      const int ns_blk = n_ctx + (len + BN - 1) / BN;
+      const int R = (len + TOK - 1) / TOK;
+      const int n_keep = keep_out ? (m > 0 ? n_ctx : (l0 + BN - 1) / BN) : 0;
+      set_mode(2);
+      for (int s = ns_blk - 1; s >= (keep_in ? n_ctx : 0); --s) {
+        drain(s);
+        const int lo = s < n_ctx ? s0 + s * BN : start + (s - n_ctx) * BN;
+        if (leader) {
+          ptx::mbar_expect_tx(bar(kKVFull + s), kSlotBytes);
+          load_slot(s, s, g, b, lo);
+        }
+        out_mask |= 1u << s;
+      }
+      Job it;
+      it.b = b; it.g = g; it.m = m; it.chunk = 0;
+      it.start = start; it.len = len;
+      it.ctx_lo = s0; it.ctx_hi = s0 + ctx; it.n_ctx = n_ctx; it.j0 = 0;
+      it.tile0 = 0;
+      auto slots_of = [&](int i) { return n_ctx + (min(len, (R - i) * TOK) + BN - 1) / BN; };  // i-th largest tile
+      for (int i = 0; i < R; ++i) {
+        const int x = deal_chain(i), r = R - 1 - i;
+        it.t0 = r * TOK;
+        it.own_n = min(len, it.t0 + TOK);
+        it.n = slots_of(i);
+        const bool first = i < 2;
+        const int nx = deal_next(i);
+        const int rel_lo = max(n_keep, nx < R ? slots_of(nx) : 0);  // slots kept for the next block are never handed back
+        const int rel_hi = first ? ns_blk : it.n;
+        it.flags = kFDoc | (first ? kFFirst : 0) | (keep_in ? kFKeep : 0);
+        it.aux = rel_lo | (rel_hi << 8);
+        publish(x, it);
+        load_q(x, g, b, start + it.t0);
+      }
+      if (R == 1) {  // chain 1 has no row tile: it only hands the slots back
+        it.t0 = 0; it.own_n = 0; it.n = 0;
+        it.flags = kFDoc | kFFirst | (keep_in ? kFKeep : 0);
+        it.aux = n_keep | (ns_blk << 8);
+        publish(1, it);
+      }
+    };
+
+    // The work list is handed out dynamically: whichever CTA is free claims the next index.  Claims
+    // run two items ahead and the block spans of a claimed item one item ahead, so neither the
+    // atomic nor the loads are waited for.
+    auto claim = [&]() {
+      int v = 0;
+      if (leader) v = atomicAdd(a.work_counter, 1);
+      return __shfl_sync(0xffffffffu, v, 0);
+    };
+    int idx = claim(), idx_next = claim();
+    ItemRaw raw_next = load_item(a, idx, lane);
+    for (; idx < a.total_items; idx = idx_next, idx_next = claim()) {
+      const ItemRaw raw = raw_next;
+      raw_next = load_item(a, idx_next, lane);  // in flight while this item is processed
+      if (raw.kind == 0) {
+        run_pair(raw.b, raw.g, raw.m, raw.chunk, raw.p, raw.start, raw.len, raw.s0, raw.l0, raw.s2, raw.l2);
+        continue;
+      }
+      auto fits = [&](int m, int len) {
+        const int ctx = m > 0 ? raw.l0 : 0;
+        return (ctx + BN - 1) / BN + (len + BN - 1) / BN <= kSlots;
+      };
+      bool kept = false;
+      for (int i = 0; i < raw.cnt; ++i) {
+        const int m = raw.m + i;
+        const int start = __shfl_sync(0xffffffffu, raw.start, i), len = __shfl_sync(0xffffffffu, raw.len, i);
+        const int len_nx = __shfl_sync(0xffffffffu, raw.len, (i + 1) & 31);
+        if (len <= 0) continue;  // an empty block has no rows
+        if (fits(m, len)) {
+          const bool keep_out = i + 1 < raw.cnt && len_nx > 0 && fits(m + 1, len_nx) && raw.l0 > 0;
+          run_block(raw.b, raw.g, m, start, len, raw.s0, raw.l0, kept, keep_out);
+          kept = keep_out;
+        } else {
+          const int pairs = (len + 2 * TOK - 1) / (2 * TOK);
+          for (int p = 0; p < pairs; ++p)
+            run_pair(raw.b, raw.g, m, 0, p, start, len, raw.s0, raw.l0, raw.s2, raw.l2);
         }
       }
-      publish(it, kRecStop);  // end of this CTA's work list
     }
-  } else if (warp == 9) {
-    // =============================== MMA issuer =================================================
+    Job stop{};
+    stop.flags = kFStop;
+    publish(0, stop);
+    publish(1, stop);
+  } else if (warp == 9 || warp == 10) {
+    // =============================== MMA issuer of chain x ======================================
     // Whole-warp control flow, one issuing lane (always the same one: tcgen05.commit tracks the
-    // MMAs of the thread that executes it).
-    {
-      const bool leader = lane == 0;
-      uint32_t kv_cnt = 0, q_uses[2] = {0, 0}, p_seen[2] = {0, 0}, items_done[2] = {0, 0};
-      // Descriptors are built once: every operand buffer has a fixed address, and stepping along K
-      // or to another ring stage only adds a constant to the 16-byte-unit start-address field.
-      const uint32_t idesc_pv = ptx::idesc_bf16(BM, HD, 0, 1);
-      const uint32_t idesc_qk0 = ptx::idesc_bf16(BM, 0, 0, 0);
-      const uint64_t q_desc0 = ptx::smem_desc_sw128(sbase + kOffQ, 16, 1024);
-      const uint64_t k_desc0 = ptx::smem_desc_sw128(sbase + kOffKV, 16, 1024);
-      const uint64_t v_desc0 = ptx::smem_desc_sw128(sbase + kOffKV + kKBytes, BT * 128, 1024);
-      // keys of tile t that chain x (seeing n_vis slots) multiplies: full first slot + the valid part of the last one
-      auto tile_keys = [&](const Item& it, int t, int n_vis) {
-        const int cnt = min(2, n_vis - 2 * t);
+    // MMAs of the thread that executes it).  The two chains' issuers never wait for each other;
+    // they only meet in the kKVFree barriers (two arrivals hand a slot back to the TMA warp).
+    const int x = warp - 9;
+    const bool leader = lane == 0;
+    uint32_t q_uses = 0, p_seen = 0, jobs_done = 0;
+    uint32_t full_par = 0;  // bit s: parity of the next kKVFull+s phase this warp has not consumed yet
+    int blk_waited = 0;     // resident block: slots [0, blk_waited) have landed
+    // Descriptors are built once: every operand buffer has a fixed address, and stepping along K
+    // or to another slot only adds a constant to the 16-byte-unit start-address field.
+    const uint32_t idesc_pv = ptx::idesc_bf16(BM, HD, 0, 1);
+    const uint32_t idesc_qk0 = ptx::idesc_bf16(BM, 0, 0, 0);
+    const uint64_t q_desc0 = ptx::smem_desc_sw128(sbase + kOffQ + (uint32_t)x * kQBytes, 16, 1024);
+    const uint64_t k_desc0 = ptx::smem_desc_sw128(sbase + kOffK, 16, 1024);
+    const uint64_t v_desc0 = ptx::smem_desc_sw128(sbase + kOffV, kPoolHalf, 1024);
+    const uint32_t tm_s = tmem + (uint32_t)x * kChainCols, tm_o = tm_s + kColO;
+    auto wait_full = [&](int s) {
+      wait(kKVFull + s, (full_par >> s) & 1u, 22 + x);
+      full_par ^= 1u << s;
+    };
+    // S = Q K^T against `keys` keys starting at pool slot `slot`
+    auto issue_qk = [&](int slot, int keys, bool last) {
+      const uint32_t idesc = idesc_qk0 | ((uint32_t)((keys + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
+      const uint32_t a_lo = (uint32_t)q_desc0, a_hi = (uint32_t)(q_desc0 >> 32);
+      const uint32_t b_lo = (uint32_t)k_desc0 + (uint32_t)slot * (kSlotHalf >> 4), b_hi = (uint32_t)(k_desc0 >> 32);
+      if (leader) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
+          const uint32_t boff = (uint32_t)(ks >> 2) * (kPoolHalf >> 4) + (uint32_t)(ks & 3) * 2;
+          ptx::mma_ss_lohi(tm_s, a_lo + aoff, a_hi, b_lo + boff, b_hi, idesc, ks > 0);
+        }
+        ptx::mma_commit(bar(kSFull + x));
+        if (last) ptx::mma_commit(bar(kQFree + x));  // last read of this chain's Q tile
+      }
+    };
+    // O (+)= P V over `keys` keys starting at pool slot `slot`; P sits over the first 64 columns of S
+    auto issue_pv = [&](int slot, int keys, bool first) {
+      const uint32_t b_lo = (uint32_t)v_desc0 + (uint32_t)slot * (kSlotHalf >> 4), b_hi = (uint32_t)(v_desc0 >> 32);
+      const int ksteps = (keys + 15) >> 4;
+      if (leader) {
+#pragma unroll
+        for (int ks = 0; ks < BT / 16; ++ks)
+          if (ks < ksteps)
+            ptx::mma_ts_lohi(tm_o, tm_s + (uint32_t)ks * 8, b_lo + (uint32_t)ks * ((16 * 128) >> 4), b_hi, idesc_pv,
+                             (!first || ks > 0) ? 1u : 0u);
+        ptx::mma_commit(bar(kPVDone + x));
+      }
+    };
+    for (uint32_t job_no = 0;; ++job_no) {
+      const Job it = next_job(x, job_no);
+      if (it.flags & kFStop) break;
+      const int n = it.n, T = (n + 1) >> 1;
+      // Every tile but the last spans 128 keys (a short context slot inside a tile is masked by the
+      // softmax, not trimmed); the last one is computed once here, off the per-tile path.
+      int last_keys = 0;
+      if (T > 0) {
+        const int cnt = min(2, n - 2 * (T - 1));
         int nk, own_off; bool own;
-        tile_lo(it, 2 * t + cnt - 1, nk, own, own_off);
-        return (cnt - 1) * BN + nk;
-      };
-      auto issue_qk = [&](int x, int keys, bool last, uint32_t st) {
-        const uint32_t idesc = idesc_qk0 | ((uint32_t)((keys + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
-        const uint32_t a_lo = (uint32_t)q_desc0 + (uint32_t)x * (kQBytes >> 4);
-        const uint32_t b_lo = (uint32_t)k_desc0 + st * (kStageBytes >> 4);
-        const uint32_t a_hi = (uint32_t)(q_desc0 >> 32), b_hi = (uint32_t)(k_desc0 >> 32);
-        const uint32_t d = tmem + (uint32_t)x * kChainCols;
-        if (leader) {
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
-            const uint32_t boff = (uint32_t)(ks >> 2) * ((BT * 128) >> 4) + (uint32_t)(ks & 3) * 2;
-            ptx::mma_ss_lohi(d, a_lo + aoff, a_hi, b_lo + boff, b_hi, idesc, ks > 0);
+        tile_lo(it, 2 * (T - 1) + cnt - 1, nk, own, own_off);
+        last_keys = (cnt - 1) * BN + nk;
+      }
+      auto keys_of = [&](int t) { return t + 1 < T ? BT : last_keys; };
+      if (T > 0) { wait(kQFull + x, q_uses, 20 + x); ++q_uses; }
+      if (it.flags & kFDoc) {
+        // ---- resident block: tile t = pool slots 2t, 2t+1; slots land once per block ----
+        if (it.flags & kFFirst) blk_waited = (it.flags & kFKeep) ? it.n_ctx : 0;
+        auto ensure = [&](int ns) {
+          while (blk_waited < ns) { wait_full(blk_waited); ++blk_waited; }
+        };
+        if (T > 0) {
+          ensure(min(n, 2));
+          ptx::tc_fence_after_sync();
+          issue_qk(0, keys_of(0), T == 1);
+          for (int t = 0; t < T; ++t) {
+            wait(kPFull + x, p_seen, 24 + x);
+            ++p_seen;
+            if (t == 0 && jobs_done > 0) wait(kOFree + x, jobs_done - 1, 26 + x);
+            ptx::tc_fence_after_sync();
+            issue_pv(2 * t, keys_of(t), t == 0);
+            if (t + 1 < T) {
+              // the chain's next S tile: queued behind the P V that reads P out of the same columns
+              ensure(min(n, 2 * t + 4));
+              ptx::tc_fence_after_sync();
+              issue_qk(2 * t + 2, keys_of(t + 1), t + 2 == T);
+            }
           }
-          ptx::mma_commit(bar(kSFull + x));
-          if (last) ptx::mma_commit(bar(kQFree + x));  // last read of this chain's Q tile
+          ++jobs_done;
         }
-      };
-      auto issue_pv = [&](int x, int keys, bool first, uint32_t st) {
-        const uint32_t pa = tmem + (uint32_t)x * kChainCols;  // P sits over the first 64 columns of S
-        const uint32_t b_lo = (uint32_t)v_desc0 + st * (kStageBytes >> 4), b_hi = (uint32_t)(v_desc0 >> 32);
-        const uint32_t d = tmem + (uint32_t)x * kChainCols + kColO;
-        const int ksteps = (keys + 15) >> 4;
-        if (leader) {
-#pragma unroll
-          for (int ks = 0; ks < BT / 16; ++ks)
-            if (ks < ksteps)
-              ptx::mma_ts_lohi(d, pa + (uint32_t)ks * 8, b_lo + (uint32_t)ks * ((16 * 128) >> 4), b_hi, idesc_pv, (!first || ks > 0) ? 1u : 0u);
-          ptx::mma_commit(bar(kPVDone + x));
-        }
-      };
-      for (uint32_t item_no = 0;; ++item_no) {
-        int flags;
-        const Item it = next_item(item_no, flags);
-        if (flags & kRecStop) break;
-        const int n0 = it.n_0, n1 = it.n_1;
-        const int T0 = (n0 + 1) >> 1, T1 = (n1 + 1) >> 1, T = (it.n_tiles + 1) >> 1;
-        // Every tile but a chain's last spans 128 keys (a short context slot inside a tile is masked by
-        // the softmax, not trimmed); the last one is computed once here, off the per-tile path.
-        const int last_keys0 = T0 > 0 ? tile_keys(it, T0 - 1, n0) : 0, last_keys1 = T1 > 0 ? tile_keys(it, T1 - 1, n1) : 0;
-        auto keys_of = [&](int x, int t) { return t + 1 < (x == 0 ? T0 : T1) ? BT : (x == 0 ? last_keys0 : last_keys1); };
-#pragma unroll
-        for (int x = 0; x < 2; ++x)
-          if ((x == 0 ? n0 : n1) > 0) { wait(kQFull + x, q_uses[x], 20 + x); ++q_uses[x]; }
+        // hand back the slots no later job of this chain in this block needs
+        // (every load of the block is consumed by both issuers, also of slots this chain never reads or
+        // that stay resident for the next block: the phase parities must not fall behind)
+        const int rel_lo = it.aux & 0xff, rel_hi = (it.aux >> 8) & 0xff;
+        ensure(rel_hi);
+        for (int s = rel_lo; s < rel_hi; ++s)
+          if (leader) ptx::mma_commit(bar(kKVFree + s));
+      } else {
+        // ---- streamed pair: tile t sits in ring position (tile0 + t) & 1 = pool slots 0-1 or 2-3 ----
+        const int Ti = it.aux;  // tiles of the item; this chain computes on the first T of them
         int kv_waited = -1;
         auto need_kv = [&](int t) {
           if (kv_waited >= t) return;
-          const uint32_t gidx = kv_cnt + (uint32_t)t;
-          wait(kKVFull + gidx % kStages, gidx / kStages, 22);
+          wait_full(2 * ((it.tile0 + t) & 1));
           kv_waited = t;
         };
-        need_kv(0);
-        ptx::tc_fence_after_sync();
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          const int Tx = x == 0 ? T0 : T1;
-          if (Tx > 0) issue_qk(x, keys_of(x, 0), Tx == 1, kv_cnt % kStages);
+        if (T > 0) {
+          need_kv(0);
+          ptx::tc_fence_after_sync();
+          issue_qk(2 * (it.tile0 & 1), keys_of(0), T == 1);
         }
-        for (int t = 0; t < T; ++t) {
-          const uint32_t st = (kv_cnt + (uint32_t)t) % kStages;
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            const int Tx = x == 0 ? T0 : T1;
-            if (t >= Tx) continue;
-            wait(kPFull + x, p_seen[x], 24 + x);
-            ++p_seen[x];
-            if (t == 0 && items_done[x] > 0) wait(kOFree + x, items_done[x] - 1, 26 + x);
+        for (int t = 0; t < Ti; ++t) {
+          const int slot = 2 * ((it.tile0 + t) & 1);
+          if (t < T) {
+            wait(kPFull + x, p_seen, 24 + x);
+            ++p_seen;
+            if (t == 0 && jobs_done > 0) wait(kOFree + x, jobs_done - 1, 26 + x);
             ptx::tc_fence_after_sync();
-            issue_pv(x, keys_of(x, t), t == 0, st);
-            if (t + 1 < Tx) {
-              // the chain's next S tile: queued behind the P V that reads P out of the same columns
-              need_kv(t + 1);
-              ptx::tc_fence_after_sync();
-              issue_qk(x, keys_of(x, t + 1), t + 2 == Tx, (kv_cnt + (uint32_t)t + 1) % kStages);
-            }
+            issue_pv(slot, keys_of(t), t == 0);
+          } else {
+            need_kv(t);  // not visible to this chain: consume the phase, then hand the tile back
           }
-          if (leader) ptx::mma_commit(bar(kKVFree + st));  // both chains' MMAs on this stage are queued
+          if (leader) ptx::mma_commit(bar(kKVFree + slot));
+          if (t + 1 < T) {
+            need_kv(t + 1);
+            ptx::tc_fence_after_sync();
+            issue_qk(2 * ((it.tile0 + t + 1) & 1), keys_of(t + 1), t + 2 == T);
+          }
         }
-        kv_cnt += (uint32_t)T;
-#pragma unroll
-        for (int x = 0; x < 2; ++x)
-          if ((x == 0 ? n0 : n1) > 0) ++items_done[x];
+        if (T > 0) ++jobs_done;
       }
     }
   } else {
@@ -570,19 +729,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)x * kChainCols;
     uint32_t s_seen = 0, pv_seen = 0;
 
-    for (uint32_t item_no = 0;; ++item_no) {
-      int flags;
-      const Item it = next_item(item_no, flags);
-      if (flags & kRecStop) break;
-      if (it.n_x(x) == 0) continue;
+    for (uint32_t job_no = 0;; ++job_no) {
+      const Job it = next_job(x, job_no);
+      const int flags = it.flags;
+      if (flags & kFStop) break;
+      if (it.n == 0) continue;
       const int32_t* bs = a.blk_start + (size_t)it.b * a.M;
       const int32_t* bl = a.blk_len + (size_t)it.b * a.M;
-      const int tok = it.t0(x) + (r >> a.g_shift);
+      const int tok = it.t0 + (r >> a.g_shift);
       const int n = it.g * G + (r & (G - 1));
       const bool active = tok < it.len;
-      const bool ctx_check = (flags & kRecCtxCheck) != 0;  // the query block's context contains padding slots
+      const bool ctx_check = (flags & kFCtxCheck) != 0;  // the query block's context contains padding slots
       float m_run = -INFINITY, l_run = 0.f;
-      const int n_mine = it.n_x(x);
+      const int n_mine = it.n;
+      const bool split = (flags & kFSplit) != 0;
       const int t_mine = (n_mine + 1) >> 1;
 
       for (int t = 0; t < t_mine; ++t) {
@@ -613,10 +773,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           // between are masked element by element.  Padded context ranges (reference layout with
           // gaps between blocks) take the general per-element path.
           int lim = BN, lim_lo = BN, lim_hi = BN;
-          if (nk < BN || (own && own_off + BN - 1 > it.t0(x)) || (!own && ctx_check)) {
+          const bool premasked = !own && ctx_check;  // padded context: columns masked one by one from the slot-validity ballots
+          if (nk < BN || (own && own_off + BN - 1 > it.t0) || premasked) {
             lim = nk;
             if (own) lim = max(0, min(nk, tok - own_off + 1));
-            if (!own && ctx_check) {
+            if (premasked) {
               const unsigned v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
               const unsigned v1 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + 32 + lane));
 #pragma unroll
@@ -624,6 +785,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
                 sr[c] = ok ? sr[c] : 0xff800000u;  // -inf
               }
+              lim_lo = 0;  // every group takes the masked form below (masked columns get P = 0 exactly)
             } else {
               lim_lo = __reduce_min_sync(0xffffffffu, lim);
               lim_hi = __reduce_max_sync(0xffffffffu, lim);
@@ -640,7 +802,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               if (!kGrouped || c0 < lim_hi) {
                 if (kGrouped && c0 + 8 > lim_lo) {
 #pragma unroll
-                  for (int c = c0; c < c0 + 8; ++c) sr[c] = c < lim ? sr[c] : 0xff800000u;  // -inf
+                  for (int c = c0; c < c0 + 8; ++c) sr[c] = (c < lim || premasked) ? sr[c] : 0xff800000u;  // -inf
                 }
 #pragma unroll
                 for (int c = c0; c < c0 + 8; c += 2)
@@ -708,8 +870,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                   const float p0 = ptx::ex2(t0), p1 = ptx::ex2(t1);
                   const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
                   ptx::unpack2(p23, p2, p3);
+                  if (kGrouped && c0 + 8 > lim_lo) {
+                    // a masked column must contribute exactly nothing: the polynomial maps -inf to 2^-126,
+                    // which times a huge (finite) value in a padding slot of V would still be visible
+                    p2 = sr[c + 2] == 0xff800000u ? 0.f : p2;
+                    p3 = sr[c + 3] == 0xff800000u ? 0.f : p3;
+                    ps2[1] = ptx::add2(ps2[1], ptx::pack2(p2, p3));
+                  } else {
+                    ps2[1] = ptx::add2(ps2[1], p23);
+                  }
                   ps2[0] = ptx::add2(ps2[0], ptx::pack2(p0, p1));
-                  ps2[1] = ptx::add2(ps2[1], p23);
                   __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
                   pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
                   pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
@@ -742,7 +912,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // chunk is in flight while the current one is converted and stored.
       uint32_t obuf[2][32];
       ptx::tmem_ld32(tmem_lane + kColO, obuf[0]);
-      if (it.split) {
+      if (split) {
         // un-normalised partial (O, max, sum) of this key chunk; merged by attn_combine_kernel
         const bool wr = active && tok < a.lq_max;
         const int64_t prow = (((int64_t)it.b * a.N + n) * a.lq_max + tok) * a.n_split + it.chunk;
@@ -818,6 +988,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
 // Merge the key-chunk partials of the query block: one warp per (prompt, head, query token).
 __global__ void __launch_bounds__(128) attn_combine_kernel(TcArgs a) {
+  if (a.hdr[1] != 0) return;
   const int lane = threadIdx.x & 31;
   const int64_t w = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int64_t total = (int64_t)a.B * a.N * a.lq_max;
@@ -850,30 +1021,81 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(TcArgs a) {
   if (a.lse != nullptr && lane == 0) a.lse[((int64_t)b * a.N + n) * a.S + start + tok] = (ref + log2f(l)) * 0.6931471805599453f;
 }
 
-// neutral partials for chunks that own no tile (the combine step skips sum == 0)
-__global__ void attn_clear_partials_kernel(float2* ml, int64_t n, int* work_counter) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i == 0) *work_counter = 0;
-  if (i < n) ml[i] = make_float2(-INFINITY, 0.f);
-}
-
 }  // namespace
 
-// Key chunks for the query block.  Its context is every earlier token of the prompt (S is the only
-// bound known on the host), walked 64 keys per step per row tile; cutting it into chunks of about
-// 1024 keys keeps that serial chain short and spreads it over the SMs.
-constexpr size_t kWsHeader = 256;  // workspace: [work counter, padding][partial O][partial (max, sum)]
+// The give-up path of the kernels' bounded waits, exercised without a fault: one thread waits, with a small
+// budget, on an mbarrier that nothing ever arrives at; the wait runs out, the thread records kStatusSelfTest in
+// the caller's status word exactly as attn_tc_kernel's waits do, and the kernel returns normally.
+__global__ void selftest_wait_kernel(int32_t* status, uint32_t budget) {
+  __shared__ __align__(8) uint64_t mbar;
+  const uint32_t b = ptx::smem_u32(&mbar);
+  ptx::mbar_init(b, 1);
+  ptx::fence_barrier_init();
+  if (!ptx::mbar_wait(b, 0, budget)) atomicCAS(status, 0, kStatusSelfTest);
+}
 
+int selftest_wait_launch(int32_t* status, uint32_t budget, cudaStream_t st) {
+  selftest_wait_kernel<<<1, 1, 0, st>>>(status, budget);
+  BRK_CUDA(cudaGetLastError());
+  return BRK_OK;
+}
+
+// Launched in front of either attention kernel.  Block 0 checks the block spans (inside [0, S), no longer than
+// max_block_len, ordered, not overlapping) and records the verdict in the workspace header -- a non-zero hdr[1]
+// makes the attention kernels return without touching memory, and the caller's status word (if any) gets
+// kStatusBadSpans.  All blocks reset the work counter and the query block's partial (max, sum) pairs to neutral.
+__global__ void attn_prologue_kernel(const int32_t* __restrict__ blk_start, const int32_t* __restrict__ blk_len, int B,
+                                     int M, int S, int max_block_len, int max_query_len, int* hdr, int32_t* status,
+                                     float2* ml, int64_t n_ml) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_ml) ml[i] = make_float2(-INFINITY, 0.f);
+  if (blockIdx.x != 0) return;
+  __shared__ int bad;
+  if (threadIdx.x == 0) {
+    bad = 0;
+    hdr[0] = 0;
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < B * M; j += blockDim.x) {
+    const int m = j % M;
+    const int s = blk_start[j], l = blk_len[j];
+    bool ok = s >= 0 && l >= 0 && l <= max_block_len && s <= S - l;
+    if (ok && m > 0) ok = blk_start[j - 1] >= 0 && blk_len[j - 1] >= 0 && blk_start[j - 1] <= s - blk_len[j - 1];
+    if (ok && m == M - 1 && max_query_len > 0) ok = l <= max_query_len;
+    if (!ok) bad = 1;  // benign race: every writer stores the same value
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    hdr[1] = bad;
+    if (bad && status) atomicCAS(status, 0, kStatusBadSpans);
+  }
+}
+
+int attn_prologue_launch(const brk_attn_params& p, int* hdr, float2* ml, int64_t n_ml, cudaStream_t st) {
+  const unsigned blocks = (unsigned)(n_ml > 0 ? (n_ml + 255) / 256 : 1);
+  attn_prologue_kernel<<<blocks, 256, 0, st>>>(p.blk_start, p.blk_len, p.B, p.M, p.S, p.max_block_len, p.max_query_len,
+                                               hdr, p.status, ml, n_ml);
+  BRK_CUDA(cudaGetLastError());
+  return BRK_OK;
+}
+
+// Key chunks for the query block.  Its context is every earlier token of the prompt (S is the only
+// bound known on the host), walked 128 keys per step per row tile; cutting it into chunks of about
+// 1024 keys keeps that serial chain short and spreads it over the SMs.
 static int tc_splits(const brk_attn_params& p) {
   if (p.M < 2) return 1;
   int n = (p.S + 1023) / 1024;
   return n < 1 ? 1 : (n > 32 ? 32 : n);
 }
 
+static int query_rows(const brk_attn_params& p) {
+  return (p.max_query_len > 0 && p.max_query_len < p.max_block_len) ? p.max_query_len : p.max_block_len;
+}
+
 size_t attn_tc_workspace(const brk_attn_params& p) {
   const int ns = tc_splits(p);
-  if (ns <= 1) return kWsHeader;  // the work counter
-  const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
+  if (ns <= 1) return kWsHeader;  // work counter and span verdict
+  const size_t rows = (size_t)p.B * p.N * query_rows(p) * ns;
   return kWsHeader + rows * HD * sizeof(float) + rows * sizeof(float2);
 }
 
@@ -890,8 +1112,12 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   int gs = 0;
   while ((1 << gs) < G) ++gs;
   const int TOK = BM / G;
-  const int pairs = (p.max_block_len + 2 * TOK - 1) / (2 * TOK);
-  const int64_t total_items = (int64_t)p.B * p.Nk * pairs * (ns + p.M - 1);
+  const int lq = query_rows(p);
+  const int pairs_q = (lq + 2 * TOK - 1) / (2 * TOK);
+  const int n_groups = p.M > 1 ? (p.M - 1 + kGroup - 1) / kGroup : 0;
+  const int64_t nbg = (int64_t)p.B * p.Nk;
+  const int64_t sec1 = nbg * ns * pairs_q;
+  const int64_t total_items = sec1 + nbg * n_groups;
   BRK_REQUIRE(total_items < (1ll << 30), BRK_E_UNSUPPORTED, "too many work items (%lld)", (long long)total_items);
   CUtensorMap tq, tk, tv;
   int rc;
@@ -915,39 +1141,35 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   a.blk_start = p.blk_start;
   a.blk_len = p.blk_len;
   a.status = p.status;
+  a.hdr = reinterpret_cast<const int*>(ws);
   a.B = p.B; a.N = p.N; a.Nk = p.Nk; a.S = p.S; a.M = p.M;
   a.G = G; a.g_shift = gs;
   a.scale_log2 = p.scale * 1.4426950408889634f;
   a.n_split = ns;
-  a.lq_max = p.max_block_len;
-  a.pairs = pairs;
+  a.lq_max = lq;
+  a.pairs_q = pairs_q;
+  a.n_groups = n_groups;
   a.o_align32 = (((uintptr_t)p.o.ptr & 31) == 0 && p.o.stride_b % 16 == 0 && p.o.stride_h % 16 == 0 && p.o.stride_s % 16 == 0) ? 1 : 0;
+  a.sec1 = (int)sec1;
   a.total_items = (int)total_items;
-  a.div_sec1 = make_fastdiv((uint32_t)(p.B * p.Nk * ns));
-  a.div_nbg = make_fastdiv((uint32_t)(p.B * p.Nk));
-  a.div_sec2 = make_fastdiv((uint32_t)(p.B * p.Nk * (p.M > 1 ? p.M - 1 : 1)));
+  a.div_sec1 = make_fastdiv((uint32_t)(nbg * ns));
+  a.div_nbg = make_fastdiv((uint32_t)nbg);
   a.div_nk = make_fastdiv((uint32_t)p.Nk);
-  const size_t rows = (size_t)p.B * p.N * p.max_block_len * ns;
+  const size_t rows = (size_t)p.B * p.N * lq * ns;
   float* const part = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kWsHeader);
   a.work_counter = reinterpret_cast<int*>(ws);
   a.part_o = ns > 1 ? part : nullptr;
   a.part_ml = ns > 1 ? reinterpret_cast<float2*>(part + rows * HD) : nullptr;
-  {
-    const int64_t n_clear = ns > 1 ? (int64_t)rows : 0;  // always launched: it also resets the work counter
-    attn_clear_partials_kernel<<<(unsigned)(n_clear > 0 ? (n_clear + 255) / 256 : 1), 256, 0, st>>>(a.part_ml, n_clear, a.work_counter);
-    BRK_CUDA(cudaGetLastError());
-  }
+  if ((rc = attn_prologue_launch(p, reinterpret_cast<int*>(ws), a.part_ml, ns > 1 ? (int64_t)rows : 0, st))) return rc;
   const int grid = (int)(total_items < sms[dev] ? total_items : sms[dev]);
   attn_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, a);
   BRK_CUDA(cudaGetLastError());
   if (ns > 1) {
-    const int64_t warps = (int64_t)p.B * p.N * p.max_block_len;
+    const int64_t warps = (int64_t)p.B * p.N * lq;
     attn_combine_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(a);
     BRK_CUDA(cudaGetLastError());
   }
   return BRK_OK;
 }
-
-
 
 }  // namespace brk

@@ -43,6 +43,8 @@ static int check_attn(const brk_attn_params* p) {
   BRK_REQUIRE(p->max_block_len > 0 && p->max_block_len <= p->S, BRK_E_ARG, "max_block_len=%d out of range (S=%d)",
               p->max_block_len, p->S);
   BRK_REQUIRE(p->blk_start && p->blk_len, BRK_E_ARG, "block spans are null");
+  BRK_REQUIRE(p->max_query_len >= 0 && p->max_query_len <= p->S, BRK_E_ARG, "max_query_len=%d out of range (S=%d)",
+              p->max_query_len, p->S);
   int rc;
   if ((rc = check_view(p->q, p->dtype, "q"))) return rc;
   if ((rc = check_view(p->k, p->dtype, "k"))) return rc;
@@ -84,17 +86,40 @@ int brk_spans_from_mask(const uint8_t* mask, int32_t B, int32_t M, int32_t H, in
 
 size_t brk_attn_fwd_workspace_bytes(const brk_attn_params* p) {
   if (p == nullptr) return 0;
-  return resolve_algo(p) == BRK_ALGO_TC ? attn_tc_workspace(*p) : 0;
+  return resolve_algo(p) == BRK_ALGO_TC ? attn_tc_workspace(*p) : kWsHeader;
 }
 
 int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int rc = check_attn(p);
   if (rc) return rc;
   const int algo = resolve_algo(p);
-  if (algo == BRK_ALGO_SIMT) return attn_simt_launch(*p, (cudaStream_t)stream);
+  if (algo == BRK_ALGO_SIMT) return attn_simt_launch(*p, workspace, workspace_bytes, (cudaStream_t)stream);
   if (algo == BRK_ALGO_TC) return attn_tc_launch(*p, workspace, workspace_bytes, (cudaStream_t)stream);
   set_error("unknown attention algorithm %d", p->algo);
   return BRK_E_UNSUPPORTED;
+}
+
+int brk_status_poll(int32_t* status, void* stream) {
+  BRK_REQUIRE(status != nullptr, BRK_E_ARG, "status is null");
+  int32_t v = 0;
+  BRK_CUDA(cudaMemcpyAsync(&v, status, sizeof(v), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  BRK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (v == 0) return BRK_OK;
+  BRK_CUDA(cudaMemsetAsync(status, 0, sizeof(v), (cudaStream_t)stream));
+  if (v == kStatusBadSpans) {
+    set_error("malformed block spans (a block outside [0, S), longer than max_block_len / max_query_len, or "
+              "overlapping its predecessor): the attention call wrote nothing");
+    return BRK_E_ARG;
+  }
+  set_error("a bounded device-side wait gave up (code %d: %s); the outputs of that call are incomplete", v,
+            v == kStatusSelfTest ? "self-test" : v < 20 ? "TMA warp" : v < 30 ? "MMA warp" : v < 40 ? "softmax warp" : "job ring");
+  return BRK_E_TIMEOUT;
+}
+
+int brk_selftest_bounded_wait(int32_t* status, uint32_t budget, void* stream) {
+  BRK_REQUIRE(status != nullptr, BRK_E_ARG, "status is null");
+  BRK_REQUIRE(budget >= 1 && budget <= (1u << 16), BRK_E_ARG, "budget %u out of range [1, 65536]", budget);
+  return selftest_wait_launch(status, budget, (cudaStream_t)stream);
 }
 
 size_t brk_doc_scores_workspace_bytes(const brk_score_params* p) { return p ? doc_scores_workspace(*p) : 0; }

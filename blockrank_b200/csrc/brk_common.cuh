@@ -97,8 +97,18 @@ struct View {
 };
 inline View make_view(const brk_view& v) { return View{(char*)v.ptr, v.stride_b, v.stride_h, v.stride_s}; }
 
+// Every attention call gets a 256-byte header at the start of its workspace: [0] the work counter of the
+// tensor-core kernel, [1] the verdict of the span check (non-zero: malformed, the kernels write nothing).
+constexpr size_t kWsHeader = 256;
+// Values of the caller's status word: 10..49 name the bounded wait that gave up, 50 malformed block spans,
+// 90 the self-test's wait.
+constexpr int kStatusBadSpans = 50;
+constexpr int kStatusSelfTest = 90;
+
 // kernel launchers implemented in the .cu files
-int attn_simt_launch(const brk_attn_params& p, cudaStream_t st);
+int attn_prologue_launch(const brk_attn_params& p, int* hdr, float2* ml, int64_t n_ml, cudaStream_t st);
+int attn_simt_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
+int selftest_wait_launch(int32_t* status, uint32_t budget, cudaStream_t st);
 int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t attn_tc_workspace(const brk_attn_params& p);
 int sm_count();

@@ -13,12 +13,15 @@
 //                        a tcgen05 tile (M >= 64, operands staged in shared
 //                        memory, result through tensor memory) would add
 //                        latency to a kernel that has no tensor-rate problem.
-//   doc_finalize_kernel  one CTA per prompt, one warp per (head, row): merges the
-//                        per-document pairs into the softmax over all document
-//                        tokens and emits the per-document probability mass,
+//   finalize (same launch) the CTA that finishes a prompt last (a counter per prompt in the
+//                        scratch, bumped after each CTA's partials are globally visible)
+//                        merges the per-document pairs into the softmax over all
+//                        document tokens, emits the per-document probability mass and
 //                        then the mean over heads and rows / temperature.
 //   raw_scores_kernel    compatibility output: raw masked logits of the last R
 //                        slots against every slot.
+#include <atomic>
+
 #include "brk_common.cuh"
 
 namespace brk {
@@ -33,6 +36,10 @@ struct ScoreArgs {
   const int32_t* blk_start;
   const int32_t* blk_len;
   float2* partial;  // [B, N, R, nd]
+  unsigned* done;   // [B] CTAs of the prompt that have published their partials; wraps to 0 by itself
+  float* mass;      // [B, N, R, nd] out
+  float* logits;    // [B, nd] out, optional
+  float inv_count_temp;  // 1 / (N * R * temperature)
   int B, N, Nk, S, M, R;
   float scale;
 };
@@ -42,6 +49,56 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2)
   const float ref = (mn == -INFINITY) ? 0.f : mn;
   l = l * exp2f(m - ref) + l2 * exp2f(m2 - ref);
   m = mn;
+}
+
+// Called by every thread of a partial-kernel CTA after its (max, sum) pairs are written.  The CTA that
+// completes prompt b -- the last of its (documents x KV heads) CTAs to bump the prompt's counter -- finalizes
+// it.  Phase 1, one warp per (head, signal row) at a time: merge the per-document pairs into the softmax over
+// all document tokens and emit the per-document probability mass.  Phase 2 (when logits are wanted), one
+// thread per document: mean over heads and rows of the masses just written, divided by the temperature,
+// summed in a fixed order.  atomicInc wraps the counter back to 0, so the scratch is ready for the next call.
+__device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b) {
+  __shared__ int is_last;
+  __syncthreads();  // every partial of this CTA has been issued
+  if (threadIdx.x == 0) {
+    __threadfence();  // ... and is visible device-wide before the counter moves
+    const unsigned total = (unsigned)(a.M - 2) * (unsigned)a.Nk;
+    is_last = atomicInc(a.done + b, total - 1) == total - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int NR = a.N * a.R, nd = a.M - 2;
+  for (int row = warp; row < NR; row += nwarps) {
+    const size_t w = (size_t)b * NR + row;
+    const float2* p = a.partial + w * nd;
+    float mx = -INFINITY;
+    for (int d = lane; d < nd; d += 32) mx = fmaxf(mx, __ldcg(&p[d]).x);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    const float ref = (mx == -INFINITY) ? 0.f : mx;
+    float z = 0.f;
+    for (int d = lane; d < nd; d += 32) {
+      const float2 x = __ldcg(&p[d]);
+      z += x.y * exp2f(x.x - ref);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
+    const float inv = z > 0.f ? 1.f / z : 0.f;
+    for (int d = lane; d < nd; d += 32) {
+      const float2 x = __ldcg(&p[d]);
+      a.mass[w * nd + d] = x.y * exp2f(x.x - ref) * inv;
+    }
+  }
+  if (a.logits == nullptr) return;
+  __syncthreads();  // the masses of this prompt, written by this CTA, are visible to all its threads
+  for (int d = threadIdx.x; d < nd; d += blockDim.x) {
+    const float* p = a.mass + (size_t)b * NR * nd + d;
+    float acc = 0.f;
+    for (int i = 0; i < NR; ++i) acc += p[(size_t)i * nd];
+    a.logits[(size_t)b * nd + d] = acc * a.inv_count_temp;
+  }
 }
 
 // dot products of one key row against kRowBatch staged query rows
@@ -156,6 +213,7 @@ __global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
       a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
     }
   }
+  finalize_if_last(a, b);
 }
 
 __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -206,12 +264,19 @@ __global__ void __launch_bounds__(kThreads) doc_partial_mma_kernel(ScoreArgs a) 
       }
     }
     float m_lo = -INFINITY, l_lo = 0.f, m_hi = -INFINITY, l_hi = 0.f;
-    for (int base = warp * 8; base < len; base += (kThreads / 32) * 8) {
+    // The key rows of the next 8-key group are requested before the products of the current one, so a warp
+    // keeps two groups (8 x 16 bytes per lane) in flight: the kernel is bound by the latency of these loads.
+    constexpr int kStride = (kThreads / 32) * 8;
+    auto load_keys = [&](int base, uint4 (&kf)[kSteps]) {
       const int key = min(base + qr, len - 1);  // rows past the end re-read the last key; their columns are dropped below
       const __nv_bfloat16* kp = kbase + (int64_t)(start + key) * a.k.ss + 8 * j;
-      uint4 kf[kSteps];
 #pragma unroll
       for (int st = 0; st < kSteps; ++st) kf[st] = *reinterpret_cast<const uint4*>(kp + 32 * st);
+    };
+    uint4 kf[kSteps], kn[kSteps];
+    if (warp * 8 < len) load_keys(warp * 8, kf);
+    for (int base = warp * 8; base < len; base += kStride) {
+      if (base + kStride < len) load_keys(base + kStride, kn);
       float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int st = 0; st < kSteps; ++st) {
@@ -226,6 +291,8 @@ __global__ void __launch_bounds__(kThreads) doc_partial_mma_kernel(ScoreArgs a) 
           merge_ml(m_hi, l_hi, c[2 + e] * sl2, 1.f);
         }
       }
+#pragma unroll
+      for (int st = 0; st < kSteps; ++st) kf[st] = kn[st];
     }
     // the four lanes of a row, then the warps, in a fixed order
 #pragma unroll
@@ -249,41 +316,8 @@ __global__ void __launch_bounds__(kThreads) doc_partial_mma_kernel(ScoreArgs a) 
       a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
     }
   }
+  finalize_if_last(a, b);
 }
-
-// One CTA per prompt.  Phase 1, one warp per (head, signal row) at a time: merge the per-document
-// (max, sum) pairs into the softmax over all document tokens and emit the per-document probability
-// mass.  Phase 2 (when logits are wanted), one thread per document: mean over heads and rows of the
-// masses this CTA has just written, divided by the temperature, summed in a fixed order.
-__global__ void __launch_bounds__(1024) doc_finalize_kernel(const float2* __restrict__ partial, float* __restrict__ mass,
-                                                            float* __restrict__ logits, int NR, int nd,
-                                                            float inv_count_temp) {
-  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int row = warp; row < NR; row += nwarps) {
-    const size_t w = (size_t)b * NR + row;
-    const float2* p = partial + w * nd;
-    float mx = -INFINITY;
-    for (int d = lane; d < nd; d += 32) mx = fmaxf(mx, p[d].x);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    const float ref = (mx == -INFINITY) ? 0.f : mx;
-    float z = 0.f;
-    for (int d = lane; d < nd; d += 32) z += p[d].y * exp2f(p[d].x - ref);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
-    const float inv = z > 0.f ? 1.f / z : 0.f;
-    for (int d = lane; d < nd; d += 32) mass[w * nd + d] = p[d].y * exp2f(p[d].x - ref) * inv;
-  }
-  if (logits == nullptr) return;
-  __syncthreads();  // the masses of this prompt, written by this CTA, are visible to all its threads
-  for (int d = threadIdx.x; d < nd; d += blockDim.x) {
-    const float* p = mass + (size_t)b * NR * nd + d;
-    float acc = 0.f;
-    for (int i = 0; i < NR; ++i) acc += p[(size_t)i * nd];
-    logits[(size_t)b * nd + d] = acc * inv_count_temp;
-  }
-}
-
 
 // block index of a slot, or -1 for padding (blk_start is non-decreasing)
 __device__ __forceinline__ int block_of(const int32_t* bs, const int32_t* bl, int M, int s) {
@@ -347,6 +381,10 @@ ScoreArgs make_args(const brk_score_params& p) {
   a.blk_start = p.blk_start;
   a.blk_len = p.blk_len;
   a.partial = nullptr;
+  a.done = nullptr;
+  a.mass = nullptr;
+  a.logits = nullptr;
+  a.inv_count_temp = 0.f;
   a.B = p.B; a.N = p.N; a.Nk = p.Nk; a.S = p.S; a.M = p.M; a.R = p.R;
   a.scale = p.scale;
   return a;
@@ -370,21 +408,32 @@ int check(const brk_score_params& p) {
 
 }  // namespace
 
-size_t doc_scores_workspace(const brk_score_params& p) {
+// scratch layout: [B, N, R, nd] (max, sum) pairs, then B per-prompt completion counters
+static size_t partial_bytes(const brk_score_params& p) {
   const size_t nd = p.M > 2 ? p.M - 2 : 0;
   return (size_t)p.B * p.N * p.R * nd * sizeof(float2);
 }
 
-int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
+size_t doc_scores_workspace(const brk_score_params& p) {
+  return partial_bytes(p) + (((size_t)(p.B > 0 ? p.B : 0) * sizeof(unsigned) + 15) & ~(size_t)15);
+}
+
+// counters_zero: the caller guarantees that the counters are zero (they return to zero after every completed call)
+static int doc_scores_run(const brk_score_params& p, void* ws, size_t ws_bytes, bool counters_zero, cudaStream_t st) {
   int rc = check(p);
   if (rc) return rc;
   BRK_REQUIRE(p.M >= 3, BRK_E_ARG, "document scores need at least one document block (M=%d)", p.M);
   BRK_REQUIRE(p.rows && p.doc_mass, BRK_E_ARG, "rows / doc_mass must be given");
-  BRK_REQUIRE(ws != nullptr && ws_bytes >= doc_scores_workspace(p), BRK_E_WORKSPACE, "workspace %zu < %zu bytes",
-              ws_bytes, doc_scores_workspace(p));
+  BRK_REQUIRE(ws != nullptr && ws_bytes >= doc_scores_workspace(p) && ((uintptr_t)ws & 7) == 0, BRK_E_WORKSPACE,
+              "workspace %zu < %zu bytes (or not 8-byte aligned)", ws_bytes, doc_scores_workspace(p));
   BRK_REQUIRE(p.temperature > 0.f, BRK_E_ARG, "temperature must be positive");
   ScoreArgs a = make_args(p);
   a.partial = reinterpret_cast<float2*>(ws);
+  a.done = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(ws) + partial_bytes(p));
+  a.mass = p.doc_mass;
+  a.logits = p.logits;
+  a.inv_count_temp = 1.f / ((float)(p.N * p.R) * p.temperature);
+  if (!counters_zero) BRK_CUDA(cudaMemsetAsync(a.done, 0, (size_t)p.B * sizeof(unsigned), st));
   const int nd = p.M - 2, G = p.N / p.Nk;
   dim3 grid(nd, p.B * p.Nk);
   const size_t pitch = (size_t)p.D * (p.dtype == BRK_BF16 ? 2 : 4) + 16;
@@ -399,46 +448,48 @@ int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cuda
     if (p.D == 128) doc_partial_mma_kernel<128><<<grid, kThreads, 0, st>>>(a);
     else doc_partial_mma_kernel<64><<<grid, kThreads, 0, st>>>(a);
     BRK_CUDA(cudaGetLastError());
-  } else {
-    rc = p.D == 128 ? launch(doc_partial_kernel<float, 128>) : launch(doc_partial_kernel<float, 64>);
+    return BRK_OK;
   }
-  if (rc) return rc;
-  const int NR = p.N * p.R;
-  const int fin_threads = NR >= 32 ? 1024 : NR * 32;  // one warp per (head, row), 32 warps at most
-  doc_finalize_kernel<<<p.B, fin_threads, 0, st>>>(a.partial, p.doc_mass, p.logits, NR, nd,
-                                                   1.f / ((float)NR * p.temperature));
-  BRK_CUDA(cudaGetLastError());
-  return BRK_OK;
+  return p.D == 128 ? launch(doc_partial_kernel<float, 128>) : launch(doc_partial_kernel<float, 64>);
+}
+
+int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
+  return doc_scores_run(p, ws, ws_bytes, false, st);
 }
 
 // ---- allocation-free variant ----------------------------------------------------------------
-// Scratch for brk_doc_scores_static: the (max, sum) pairs that doc_partial_kernel writes and
-// doc_finalize_kernel reads live in this fixed array instead of a caller-provided workspace.
-// It is part of the library image, so every device that loads the library holds these bytes
-// until the process exits.
+// Scratch for brk_doc_scores_static: the (max, sum) pairs and the per-prompt counters live in this fixed
+// array instead of a caller-provided workspace.  It is part of the library image, so every device that
+// loads the library holds these bytes until the process exits.  The image initialises it to zero, and
+// the counters wrap back to zero at the end of every completed call, so nothing is cleared per call.
 static __device__ __align__(256) unsigned char g_static_scratch[BRK_STATIC_SCRATCH_BYTES];
 
 int doc_scores_static_launch(const brk_score_params& p, cudaStream_t st) {
+  int rc = check(p);  // argument errors are reported as such, before the size test
+  if (rc) return rc;
+  BRK_REQUIRE(p.M >= 3, BRK_E_ARG, "document scores need at least one document block (M=%d)", p.M);
   const size_t need = doc_scores_workspace(p);
   BRK_REQUIRE(need <= (size_t)BRK_STATIC_SCRATCH_BYTES, BRK_E_WORKSPACE,
-              "brk_doc_scores_static: B*N*R*(M-2)*8 = %zu bytes of scratch needed, the built-in array holds %zu; "
+              "brk_doc_scores_static: B*N*R*(M-2)*8 + 4*B = %zu bytes of scratch needed, the built-in array holds %zu; "
               "use brk_doc_scores with a caller workspace for this size",
               need, (size_t)BRK_STATIC_SCRATCH_BYTES);
   // In host code the array's name is only a handle; the kernels need its device address, which
-  // differs per device.  It is looked up once per device, with that device current.
-  static void* dev_ptr[64] = {};
+  // differs per device.  It is looked up once per device, with that device current; the cache is
+  // atomic so that two host threads making their first calls at the same time both end up with
+  // the (identical) address.
+  static std::atomic<void*> dev_ptr[64];
   int dev = 0;
   BRK_CUDA(cudaGetDevice(&dev));
   BRK_REQUIRE(dev >= 0 && dev < 64, BRK_E_UNSUPPORTED, "device ordinal %d out of range", dev);
-  if (dev_ptr[dev] == nullptr) {
-    void* ptr = nullptr;
+  void* ptr = dev_ptr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     BRK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
     BRK_REQUIRE(ptr != nullptr, BRK_E_CUDA, "cudaGetSymbolAddress returned a null scratch address");
-    dev_ptr[dev] = ptr;
+    dev_ptr[dev].store(ptr, std::memory_order_release);
   }
-  // every (prompt, head, row, document) pair is overwritten by doc_partial_kernel before
-  // doc_finalize_kernel reads it, so nothing left by an earlier call has to be cleared
-  return doc_scores_launch(p, dev_ptr[dev], (size_t)BRK_STATIC_SCRATCH_BYTES, st);
+  // every (prompt, head, row, document) pair is overwritten by the partial kernels before the finalizing CTA
+  // reads it, and the counters are back at zero, so nothing left by an earlier call has to be cleared
+  return doc_scores_run(p, ptr, (size_t)BRK_STATIC_SCRATCH_BYTES, true, st);
 }
 
 int raw_scores_launch(const brk_score_params& p, void* out, cudaStream_t st) {

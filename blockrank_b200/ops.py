@@ -63,14 +63,43 @@ def spans_from_mask(mask_bmh: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]
     return start, ln
 
 
+# One int32 status word per device, zeroed when created.  Every attention call passes it; the kernels set
+# it (first event wins) when a bounded wait gives up or the block spans are malformed, and check_status()
+# turns it into an exception at the caller's next synchronisation point.
+_status_words = {}
+
+
+def status_word(device) -> torch.Tensor:
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status_words.get(idx)
+    if t is None:
+        t = _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronise the current stream of ``device`` and raise if a kernel reported a problem since the last
+    check: BlockRankLibraryError (BRK_E_TIMEOUT) after a device-side wait gave up, ValueError (BRK_E_ARG)
+    after malformed block spans.  The word is cleared, so the next call starts clean."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(device)
+    with torch.cuda.device(w.device):
+        _lib.check(_lib.lib().brk_status_poll(w.data_ptr(), torch.cuda.current_stream(w.device).cuda_stream),
+                   "brk_status_poll")
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, blk_start: torch.Tensor, blk_len: torch.Tensor,
               scale: float, max_block_len: int, out: Optional[torch.Tensor] = None, return_lse: bool = False,
-              algo: int = _lib.ALGO_AUTO):
+              algo: int = _lib.ALGO_AUTO, max_query_len: int = 0, lse: Optional[torch.Tensor] = None):
     """BlockRank attention forward.
 
     q (B,N,S,D), k/v (B,Nk,S,D) views of any stride (head_dim contiguous);
     blk_start/blk_len int32 (B,M) on the device.  Returns out (B,S,N,D)
-    [and lse (B,N,S)].  Padding slots of ``out`` are zero.
+    [and lse (B,N,S)].  Padding slots of ``out`` are zero.  ``max_query_len``
+    (optional) bounds the last block's length and shrinks the scratch of the
+    tensor-core path.  Device-side problems (malformed spans, a wait that gave
+    up) surface at the next :func:`check_status`.
     """
     _need_cuda(q, k, v, blk_start, blk_len)
     B, N, S, D = q.shape
@@ -84,27 +113,28 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, blk_start: torc
     M = blk_start.shape[-1]
     if out is None:
         out = torch.empty(B, S, N, D, dtype=q.dtype, device=q.device)
-    lse = torch.empty(B, N, S, dtype=torch.float32, device=q.device) if return_lse else None
+    if lse is None and return_lse:
+        lse = torch.empty(B, N, S, dtype=torch.float32, device=q.device)
     p = _lib.AttnParams()
     p.dtype, p.algo = _dtype_code(q), algo
     p.B, p.N, p.Nk, p.D, p.S, p.M = B, N, Nk, D, S, M
     p.max_block_len = int(max_block_len)
+    p.max_query_len = int(max_query_len)
     p.scale = float(scale)
     p.q, p.k, p.v = _view(q), _view(k), _view(v)
     p.o = _view(out.permute(0, 2, 1, 3))
     p.lse = lse.data_ptr() if lse is not None else None
     bs, bl = blk_start.contiguous(), blk_len.contiguous()
     p.blk_start, p.blk_len = bs.data_ptr(), bl.data_ptr()
-    p.status = None
+    p.status = status_word(q.device).data_ptr()
     L = _lib.lib()
     with torch.cuda.device(q.device):
         nbytes = L.brk_attn_fwd_workspace_bytes(C.byref(p))
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
-        _lib.check(L.brk_attn_fwd(C.byref(p), ws.data_ptr() if ws is not None else None, nbytes, _stream(q)),
-                   "brk_attn_fwd")
-    # tensor-core path: reset (work counter, partials) + main kernel [+ merge of the key-chunked query block]
-    _count(1 if not nbytes else 3 if nbytes > 256 else 2)
-    return (out, lse) if return_lse else out
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        _lib.check(L.brk_attn_fwd(C.byref(p), ws.data_ptr(), nbytes, _stream(q)), "brk_attn_fwd")
+    # span check / reset kernel + main kernel [+ merge of the key-chunked query block on the tensor-core path]
+    _count(3 if nbytes > 256 else 2)
+    return (out, lse) if (return_lse or lse is not None) else out
 
 
 def _score_params(q, k, blk_start, blk_len, scale, R, temperature=0.05) -> _lib.ScoreParams:
@@ -143,16 +173,20 @@ def doc_scores(q: torch.Tensor, k: torch.Tensor, blk_start: torch.Tensor, blk_le
         nbytes = L.brk_doc_scores_workspace_bytes(C.byref(p))
         ws = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=q.device)
         _lib.check(L.brk_doc_scores(C.byref(p), ws.data_ptr(), nbytes, _stream(q)), "brk_doc_scores")
-    _count(2)  # per-document partials + per-prompt finalize (masses and logits)
+    _count(1)  # per-document partials; the CTA that completes a prompt also writes its masses and logits
     return mass, logits
 
 
 def raw_scores(q: torch.Tensor, k: torch.Tensor, blk_start: torch.Tensor, blk_len: torch.Tensor, scale: float,
-               num_last: int = 16) -> torch.Tensor:
-    """Reference-compatible second return value: (B, N, R, S) masked logits of the last R slots."""
+               num_last: int = 16, grid_h: Optional[int] = None) -> torch.Tensor:
+    """Reference-compatible second return value: (B, N, R, S) masked logits of the last R slots.
+
+    R = min(num_last, grid_h): on the reference's (M, H) grid the window never reaches past the last
+    block's H slots (src/blockrank/blockrank_std_attention.py:256-262); without a grid (padding-free
+    layout) R = min(num_last, S)."""
     _need_cuda(q, k, blk_start, blk_len)
     B, N, S, D = q.shape
-    R = min(int(num_last), S)
+    R = min(int(num_last), S if grid_h is None else int(grid_h))
     bs, bl = blk_start.contiguous(), blk_len.contiguous()
     p = _score_params(q, k, bs, bl, scale, R)
     out = torch.empty(B, N, R, S, dtype=q.dtype, device=q.device)

@@ -39,13 +39,17 @@ def partition_prompts(num_prompts: int, world_size: int, rank: int, costs: Optio
 
 
 def gather_scores(local_scores: torch.Tensor, local_ids: Sequence[int], num_prompts: int,
-                  group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+                  group: Optional[dist.ProcessGroup] = None, max_share: Optional[int] = None) -> torch.Tensor:
     """All-gather fp32 score rows and put them back in prompt order.
 
     local_scores (n_local, num_docs) for prompts ``local_ids``.  Every rank
-    receives the full (num_prompts, num_docs) tensor.  Ranks may own different
-    numbers of prompts: rows are padded to the largest share for one
-    ``all_gather_into_tensor``.
+    receives the full (num_prompts, num_docs) tensor.  One
+    ``all_gather_into_tensor`` and no host synchronisation on the regular path:
+    rows are padded to ``max_share``, the largest number of prompts any rank
+    owns, which every rank must compute the same way -- by default
+    ceil(num_prompts / world), the bound of :func:`partition_prompts` without
+    costs; pass it for a cost-balanced partition.  A prompt that no rank
+    delivered raises RuntimeError on every rank.
     """
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
         out = local_scores.new_zeros(num_prompts, local_scores.shape[1])
@@ -53,14 +57,11 @@ def gather_scores(local_scores: torch.Tensor, local_ids: Sequence[int], num_prom
         return out
     world = dist.get_world_size(group)
     nd = local_scores.shape[1]
-    cap = -(-num_prompts // world)
-    counts = [len(partition_prompts(num_prompts, world, r)) for r in range(world)]
-    cap = max(cap, len(local_ids), *counts)
-    cap_t = torch.tensor([cap], device=local_scores.device)
-    dist.all_reduce(cap_t, op=dist.ReduceOp.MAX, group=group)
-    cap = int(cap_t.item())
-    send = local_scores.new_full((cap, nd + 1), -1.0)
+    cap = int(max_share) if max_share is not None else -(-num_prompts // world)
     n = len(local_ids)
+    if n > cap:
+        raise ValueError(f"this rank owns {n} prompts but max_share is {cap}: pass the largest share of the partition")
+    send = local_scores.new_full((cap, nd + 1), -1.0)
     if n:
         send[:n, :nd] = local_scores
         send[:n, nd] = torch.as_tensor(list(local_ids), dtype=local_scores.dtype, device=local_scores.device)

@@ -119,50 +119,65 @@ class MistralPrefillRanker:
 
     # ---- forward ---------------------------------------------------------------
     @torch.no_grad()
-    def hidden_before_score_layer(self, input_ids, position_ids, blk_start, blk_len, max_block_len):
-        """Run layers 0..l*-1; returns the residual stream entering layer l*, shape (B*S, hidden).
+    def decoder_layer(self, i, h, pos, B, S, blk_start, blk_len, max_block_len, max_query_len=0):
+        """One full decoder layer ``i < score_layer`` applied in place to the residual stream ``h`` (B*S, hidden).
 
-        Both residual additions of a layer happen in the epilogue of the GEMM that produces the branch
+        Both residual additions happen in the epilogue of the GEMM that produces the branch
         (``h.addmm_``: C = C + A·B, added in fp32 before the rounding), so the branch output is never
         written to memory and the RMSNorm that follows reads one tensor instead of two."""
         c = self.cfg
-        B, S = input_ids.shape
         N, Nk, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         qd, kd = N * D, Nk * D
         T = B * S
-        pos = position_ids.reshape(T).to(torch.int32)
-        h = torch.embedding(self.embed, input_ids.reshape(T))
-        scale = D ** -0.5
-        for i in range(c.score_layer):
-            L = self.layers[i]
-            x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps)
-            qkv = torch.matmul(x, L["wqkv"].t())                         # (T, qd + 2 kd)
-            q3 = qkv[:, :qd].view(T, N, D)
-            k3 = qkv[:, qd:qd + kd].view(T, Nk, D)
-            ops.rope_(q3, k3, pos, self.inv_freq)
-            q4 = qkv[:, :qd].view(B, S, N, D).permute(0, 2, 1, 3)
-            k4 = qkv[:, qd:qd + kd].view(B, S, Nk, D).permute(0, 2, 1, 3)
-            v4 = qkv[:, qd + kd:].view(B, S, Nk, D).permute(0, 2, 1, 3)
-            ev = self._tick("attn")
-            attn = ops.attention(q4, k4, v4, blk_start, blk_len, scale, max_block_len, algo=self.algo)
-            self._tock(ev)
-            h.addmm_(attn.view(T, qd), L["wo"].t())                      # h += o_proj(attn)
-            x = ops.rmsnorm(h, L["ln2"], c.rms_norm_eps)
-            act = ops.silu_mul(torch.matmul(x, L["wgu"].t()))
-            h.addmm_(act, L["wd"].t())                                   # h += down_proj(act)
+        L = self.layers[i]
+        x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps)
+        qkv = torch.matmul(x, L["wqkv"].t())                         # (T, qd + 2 kd)
+        q3 = qkv[:, :qd].view(T, N, D)
+        k3 = qkv[:, qd:qd + kd].view(T, Nk, D)
+        ops.rope_(q3, k3, pos, self.inv_freq)
+        q4 = qkv[:, :qd].view(B, S, N, D).permute(0, 2, 1, 3)
+        k4 = qkv[:, qd:qd + kd].view(B, S, Nk, D).permute(0, 2, 1, 3)
+        v4 = qkv[:, qd + kd:].view(B, S, Nk, D).permute(0, 2, 1, 3)
+        ev = self._tick("attn")
+        attn = ops.attention(q4, k4, v4, blk_start, blk_len, D ** -0.5, max_block_len, algo=self.algo,
+                             max_query_len=max_query_len)
+        self._tock(ev)
+        h.addmm_(attn.view(T, qd), L["wo"].t())                      # h += o_proj(attn)
+        x = ops.rmsnorm(h, L["ln2"], c.rms_norm_eps)
+        act = ops.silu_mul(torch.matmul(x, L["wgu"].t()))
+        h.addmm_(act, L["wd"].t())                                   # h += down_proj(act)
         return h
 
     @torch.no_grad()
-    def score(self, input_ids, position_ids, blk_start, blk_len, max_block_len, signal_rows):
-        """input_ids/position_ids (B, S) on the device, spans int32 (B, M), signal_rows int32 (B, R).
-
-        Returns (logits (B, num_docs) fp32, doc_mass (B, N, R, num_docs) fp32).
-        """
-        c = self.cfg
+    def hidden_before_score_layer(self, input_ids, position_ids, blk_start, blk_len, max_block_len, max_query_len=0):
+        """Run layers 0..l*-1; returns the residual stream entering layer l*, shape (B*S, hidden)."""
         B, S = input_ids.shape
+        pos = position_ids.reshape(B * S).to(torch.int32)
+        h = torch.embedding(self.embed, input_ids.reshape(B * S))
+        for i in range(self.cfg.score_layer):
+            self.decoder_layer(i, h, pos, B, S, blk_start, blk_len, max_block_len, max_query_len)
+        return h
+
+    @torch.no_grad()
+    def score(self, input_ids, position_ids, blk_start, blk_len, max_block_len, signal_rows, max_query_len=0):
+        """input_ids/position_ids (B, S) on the device, spans int32 (B, M), signal_rows int32 (B, R);
+        ``max_query_len`` (optional) bounds the query block's length (smaller attention scratch).
+
+        Returns (logits (B, num_docs) fp32, doc_mass (B, N, R, num_docs) fp32).  Device-side problems
+        (malformed spans, a kernel wait that gave up) are raised by ``ops.check_status()``, which
+        :meth:`rank_host` calls after copying the scores back.
+        """
+        h = self.hidden_before_score_layer(input_ids, position_ids, blk_start, blk_len, max_block_len, max_query_len)
+        return self.score_from_hidden(h, position_ids, blk_start, blk_len, signal_rows)
+
+    @torch.no_grad()
+    def score_from_hidden(self, h, position_ids, blk_start, blk_len, signal_rows):
+        """The scoring layer's share of the work, from the residual stream ``h`` (B*S, hidden) entering it:
+        input RMSNorm, ``k_proj`` of every token, ``q_proj`` of the signal rows, RoPE, fused score epilogue."""
+        c = self.cfg
+        B, S = position_ids.shape
         N, Nk, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         R = signal_rows.shape[1]
-        h = self.hidden_before_score_layer(input_ids, position_ids, blk_start, blk_len, max_block_len)
         L = self.layers[c.score_layer]
         x = ops.rmsnorm(h, L["ln1"], c.rms_norm_eps)
         T = B * S
@@ -183,7 +198,7 @@ class MistralPrefillRanker:
 
     # ---- CUDA graphs -----------------------------------------------------------
     @torch.no_grad()
-    def score_graphed(self, input_ids, position_ids, blk_start, blk_len, max_block_len, signal_rows):
+    def score_graphed(self, input_ids, position_ids, blk_start, blk_len, max_block_len, signal_rows, max_query_len=0):
         """Same contract as :meth:`score`, but the whole launch sequence (about 440 kernels for the 7B
         architecture) is captured once per batch geometry ``(B, S, M, R, max_block_len)`` and replayed.
 
@@ -191,7 +206,8 @@ class MistralPrefillRanker:
         outputs and are overwritten by the next call with the same geometry.  The first call for a
         geometry runs eagerly twice (library initialisation, allocator warm-up) before capturing.
         """
-        key = (tuple(input_ids.shape), tuple(blk_start.shape), tuple(signal_rows.shape), int(max_block_len))
+        key = (tuple(input_ids.shape), tuple(blk_start.shape), tuple(signal_rows.shape), int(max_block_len),
+               int(max_query_len))
         cap = self._graphs.get(key)
         if cap is None:
             if self.events is not None:
@@ -201,11 +217,11 @@ class MistralPrefillRanker:
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    self.score(static[0], static[1], static[2], static[3], int(max_block_len), static[4])
+                    self.score(static[0], static[1], static[2], static[3], int(max_block_len), static[4], int(max_query_len))
             torch.cuda.current_stream(self.device).wait_stream(side)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = self.score(static[0], static[1], static[2], static[3], int(max_block_len), static[4])
+                out = self.score(static[0], static[1], static[2], static[3], int(max_block_len), static[4], int(max_query_len))
             cap = self._graphs[key] = _CapturedScore(graph, static, out)
         for dst, src in zip(cap.static, (input_ids, position_ids, blk_start, blk_len, signal_rows)):
             dst.copy_(src, non_blocking=True)
@@ -236,9 +252,12 @@ class MistralPrefillRanker:
         spans = batch["block_spans"].to(dev, non_blocking=True)
         rows = batch["signal_rows"].to(dev, non_blocking=True)
         run = self.score_graphed if self.use_graphs else self.score
-        logits, _ = run(ids, pos, spans[0], spans[1], int(batch["max_block_len"]), rows)
+        mql = int(batch["block_spans"][1, :, -1].max())  # host tensor: no synchronisation
+        logits, _ = run(ids, pos, spans[0], spans[1], int(batch["max_block_len"]), rows, mql)
         top = torch.topk(logits, k=min(k, logits.shape[-1]), dim=-1).indices
-        return logits.cpu(), top.cpu()
+        out = logits.cpu(), top.cpu()
+        ops.check_status(dev)  # raises if a kernel reported malformed spans or a wait that gave up
+        return out
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() * self.embed.element_size()

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define BRK_VERSION 100
+#define BRK_VERSION 101
 
 #if defined(__GNUC__)
 #define BRK_API __attribute__((visibility("default")))
@@ -49,7 +49,7 @@ enum {
   BRK_E_WORKSPACE = -3,  /* workspace too small */
   BRK_E_CUDA = -4,       /* a CUDA call failed (launch, attribute, tensor map) */
   BRK_E_DEVICE = -5,     /* device is not sm_100 */
-  BRK_E_TIMEOUT = -6     /* a bounded device-side wait gave up (status word set) */
+  BRK_E_TIMEOUT = -6     /* a bounded device-side wait gave up (reported by brk_status_poll) */
 };
 
 enum { BRK_BF16 = 0, BRK_F32 = 1 };
@@ -86,8 +86,19 @@ typedef struct brk_attn_params {
   float* lse;             /* optional [B, N, S] natural-log sum-exp of scaled logits; NULL to skip */
   const int32_t* blk_start; /* device, [B*M] */
   const int32_t* blk_len;   /* device, [B*M] */
-  int32_t* status;        /* optional device word; set non-zero if a bounded wait gave up */
+  int32_t* status;        /* optional device word, zeroed by the caller once; see brk_status_poll */
+  int32_t max_query_len;  /* upper bound on blk_len of the LAST block, or 0 if unknown (then max_block_len
+                             is used); a tight bound shrinks the tensor-core path's workspace */
 } brk_attn_params;
+
+/* Requirements on the data that no call can check cheaply:
+ *  - K and V must hold FINITE values in every slot the kernels may load: the slots of all blocks and up to 63
+ *    slots behind the end of any block (tiles are loaded 64 keys at a time; slots past S are never read).  Keys
+ *    outside a row's visible set get a probability of exactly zero, but 0 x Inf or 0 x NaN in V would still
+ *    poison the row.  Zero-filled or token-filled padding (what a model produces) is fine.
+ * What IS checked, on the device, by a small kernel in front of every attention call: every block lies inside
+ * [0, S), is no longer than max_block_len (the last one: max_query_len, if given), and starts at or after the end
+ * of its predecessor.  If not, the call writes nothing and the status word (if given) is set. */
 
 BRK_API int brk_version(void);
 BRK_API const char* brk_last_error(void);
@@ -102,11 +113,24 @@ BRK_API int brk_spans_from_mask(const uint8_t* mask, int32_t B, int32_t M, int32
                         int32_t* blk_start, int32_t* blk_len, void* stream);
 
 /* Device scratch the call needs (16-byte aligned; contents need not be initialised or
- * preserved between calls, but two calls in flight must not share it).  The tensor-core
- * path always needs some: a work counter, plus the partial results of the query block's
- * key chunks for long prompts.  The CUDA-core path needs none (0). */
+ * preserved between calls, but two calls in flight must not share it).  Every path needs at
+ * least a 256-byte header (work counter, verdict of the span check); the tensor-core path adds
+ * the partial results of the query block's key chunks for long prompts. */
 BRK_API size_t brk_attn_fwd_workspace_bytes(const brk_attn_params* p);
 BRK_API int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device-side status.  The kernels never trap: a bounded wait that gives up, or malformed block spans, set
+ * the caller's status word (brk_attn_params.status; first event wins) and the kernel returns normally.
+ * brk_status_poll synchronises `stream`, reads the word and clears it: BRK_OK if it was zero,
+ * BRK_E_TIMEOUT after a wait gave up (the outputs of that call are incomplete), BRK_E_ARG after malformed
+ * spans (nothing was written); brk_last_error() names the event.  Call it where the host synchronises
+ * anyway (e.g. when the scores are copied back).  No counterpart in the reference, which has no device-side
+ * error reporting. */
+BRK_API int brk_status_poll(int32_t* status, void* stream);
+/* Self-test of that give-up path: one thread waits `budget` (1..65536) polls on a barrier nothing arrives
+ * at, then records its code in *status and returns; a following brk_status_poll returns BRK_E_TIMEOUT.
+ * Nothing faults or hangs. */
+BRK_API int brk_selftest_bounded_wait(int32_t* status, uint32_t budget, void* stream);
 
 /* Fused score epilogue.  Replaces _compute_last_block_scores_kernel +
  * compute_last_block_attention_scores
@@ -118,7 +142,9 @@ BRK_API int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t works
  *   rows      device [B*R] slot indices of the signal rows (inside the query block)
  *   doc_mass  device [B, N, R, M-2] fp32 out: per head / row normalised mass per document
  *   logits    device [B, M-2] fp32 out, optional: mean over heads and rows / temperature
- * workspace: brk_doc_scores_workspace_bytes() bytes of device scratch. */
+ * workspace: brk_doc_scores_workspace_bytes() bytes of device scratch, 8-byte aligned, contents
+ * need not be initialised.  One kernel launch (plus a memset of B counters): the CTA that finishes
+ * a prompt last merges its per-document partials and writes doc_mass and logits. */
 typedef struct brk_score_params {
   int32_t dtype;
   int32_t B, N, Nk, D, S, M, R;
@@ -147,14 +173,18 @@ BRK_API int brk_doc_scores(const brk_score_params* p, void* workspace, size_t wo
  * output buffers it was given.
  *
  * Limits and rules:
- *  - B*N*R*(M-2)*8 bytes must fit in BRK_STATIC_SCRATCH_BYTES (4 MiB; e.g. 8 prompts x 32 heads
- *    x 2 rows x 1024 documents); larger problems are refused with BRK_E_WORKSPACE and a message
- *    that names both sizes.  Each GPU that loads the library holds the array until exit.
+ *  - B*N*R*(M-2)*8 + 4*B bytes (rounded up to 16) must fit in BRK_STATIC_SCRATCH_BYTES (4 MiB; e.g.
+ *    8 prompts x 32 heads x 2 rows x 1000 documents); larger problems are refused with
+ *    BRK_E_WORKSPACE and a message that names both sizes.  Each GPU that loads the library holds
+ *    the array until exit.
  *  - The first call on a device looks up the array's device address; make that first call
  *    outside any stream capture.
  *  - All calls on a device share the one array.  Nothing needs clearing between calls (every
- *    entry is rewritten before it is read), but two calls that can run at the same time on the
- *    GPU -- different streams, or different host threads -- race on it: serialise them.
+ *    (max, sum) pair is rewritten before it is read, and the per-prompt completion counters count
+ *    back to zero by the end of a call), but two calls that can run at the same time on the
+ *    GPU -- different streams, or different host threads -- race on it: serialise them.  A call
+ *    that was aborted half-way (device reset, a fault elsewhere) leaves the counters undefined.
+ *  - `stream` must belong to the device that is current when the call is made.
  *  - No cudaMalloc / cudaFree / allocating library routine is called. */
 #define BRK_STATIC_SCRATCH_BYTES (4u << 20)
 BRK_API int brk_doc_scores_static(const brk_score_params* p, void* stream);

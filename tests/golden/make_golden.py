@@ -118,7 +118,7 @@ def collate_case(ref_root):
 
 
 def tiny_model_case(std, losses):
-    """BASELINE config 1: tiny random-init Mistral, 32+10x64+32 tokens, score at layer 2, fp32 CPU."""
+    """The tiny CPU-plumbing configuration: random-init Mistral, 32+10x64+32 tokens, score at layer 2, fp32 CPU."""
     from transformers import AttentionInterface, AttentionMaskInterface, MistralConfig, MistralForCausalLM
 
     def mask_shim(*a, **kw):
@@ -193,6 +193,9 @@ def main():
                   lens=[[16, 9], [3, 16]], dtype=torch.float32)
         attn_case(std, losses, "attn_fp32_short_window", 25, B=1, N=2, Nk=1, D=64, M=4, H=16,
                   lens=[[5, 16, 2, 12]], dtype=torch.float32, num_last=4)
+        # a grid narrower than the score window: the reference returns the last block's H rows (std:256-262)
+        attn_case(std, losses, "attn_fp32_h8", 26, B=2, N=2, Nk=1, D=64, M=4, H=8,
+                  lens=[[8, 3, 8, 6], [5, 8, 1, 8]], dtype=torch.float32)
         collate_case(a.reference)
         tiny_model_case(std, losses)
 

@@ -1,5 +1,5 @@
 """GPU tests of the model-level path: runner helper kernels, the Hugging Face registry
-drop-in on the tiny Mistral (BASELINE config 1) and the early-exit runner."""
+drop-in on the tiny Mistral (the tiny CPU-plumbing configuration) and the early-exit runner."""
 import os
 
 import numpy as np

@@ -49,7 +49,8 @@ def test_additive_mask_matches_reference(golden_dir, name):
     assert torch.equal(add, torch.from_numpy(fx["add_mask"]))
 
 
-@pytest.mark.parametrize("name", ["attn_fp32_ragged", "attn_bf16_ragged", "attn_fp32_m2", "attn_fp32_short_window"])
+@pytest.mark.parametrize("name", ["attn_fp32_ragged", "attn_bf16_ragged", "attn_fp32_m2", "attn_fp32_short_window",
+                                  "attn_fp32_h8"])
 def test_raw_scores_match_reference(golden_dir, name):
     fx = load(golden_dir, name)
     q, k = torch.from_numpy(fx["q"]), torch.from_numpy(fx["k"])
@@ -118,7 +119,7 @@ def test_block_spans_and_pairs():
 
 
 def test_tiny_mistral_matches_reference(golden_dir):
-    """BASELINE config 1 end to end: rebuild the seeded HF weights, run the restated decoder."""
+    """The tiny CPU-plumbing configuration end to end: rebuild the seeded HF weights, run the restated decoder."""
     from transformers import MistralConfig, MistralForCausalLM
     fx = load(golden_dir, "tiny_mistral")
     torch.manual_seed(0)

@@ -10,6 +10,7 @@ import ctypes as C
 import pytest
 import torch
 
+from oracle import blockrank_oracle as orc
 from tests import helpers as H_
 
 pytestmark = pytest.mark.gpu
@@ -39,8 +40,9 @@ def _case(B, N, Nk, D, M, H, seed, dt):
     q, k, _ = H_.qkv(B, N, Nk, M * H, D, seed + 50, dt)
     start, ln = ops.spans_from_mask(mask.cuda())
     S = M * H
-    rows = torch.tensor([[S - 2, S - 1]] * B, dtype=torch.int32).cuda()
-    return H_.to_cuda_view(q), H_.to_cuda_view(k), start, ln, rows
+    rows = torch.tensor([[S - 2, S - 1]] * B, dtype=torch.int32)
+    exact = orc.doc_mass(q, k, mask, D ** -0.5, rows.long())   # the oracle's per-head, per-row document masses
+    return H_.to_cuda_view(q), H_.to_cuda_view(k), start, ln, rows.cuda(), exact
 
 
 def test_static_scratch_entry_matches_workspace_entry_twice():
@@ -49,7 +51,7 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
     # two calls in a row with different problems: the second must not see the first one's leftovers
     for (B, N, Nk, D, M, H, seed, dt) in [(2, 8, 2, 128, 9, 32, 41, torch.bfloat16),
                                           (1, 4, 2, 64, 5, 48, 42, torch.float32)]:
-        q, k, start, ln, rows = _case(B, N, Nk, D, M, H, seed, dt)
+        q, k, start, ln, rows, exact = _case(B, N, Nk, D, M, H, seed, dt)
         ref_mass, ref_logits = ops.doc_scores(q, k, start, ln, rows, D ** -0.5)
         mass = torch.full_like(ref_mass, float("nan"))
         logits = torch.full_like(ref_logits, float("nan"))
@@ -59,11 +61,14 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
         torch.cuda.synchronize()
         assert torch.equal(mass, ref_mass)
         assert torch.equal(logits, ref_logits)
+        # and directly against the oracle, not only against the library's other entry point
+        assert torch.allclose(mass.cpu().double(), exact, rtol=1e-3, atol=1e-6)
+        assert torch.allclose(logits.cpu().double(), exact.mean(dim=(1, 2)) / 0.05, rtol=1e-3, atol=1e-6)
 
 
 def test_static_scratch_entry_rejects_oversized_problem():
     L = _lib.lib()
-    q, k, start, ln, rows = _case(1, 4, 2, 64, 5, 48, 43, torch.float32)
+    q, k, start, ln, rows, _ = _case(1, 4, 2, 64, 5, 48, 43, torch.float32)
     mass = torch.empty(1, 4, 2, 3, device="cuda")
     logits = torch.empty(1, 3, device="cuda")
     p = _params(q, k, start, ln, rows, mass, logits, 0.125)
