@@ -83,7 +83,7 @@ constexpr int BN = 64;   // keys per slot (one TMA box)
 constexpr int BT = 128;  // keys per MMA tile (two slots)
 constexpr int HD = 128;  // head dim
 constexpr int kSlots = 5;        // 64-key K/V slots in shared memory
-constexpr int kGroup = 4;        // consecutive blocks of one (prompt, KV head) per work item
+constexpr int kMaxGroup = 4;     // consecutive blocks of one (prompt, KV head) per work item, at most
 constexpr int kThreads = 352;
 constexpr uint32_t kQBytes = 2 * BM * 128;       // one Q tile: two 64-wide halves of D
 constexpr uint32_t kSlotHalf = BN * 128;         // K (or V) of one slot, one 64-wide half of D
@@ -101,7 +101,12 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kChainCols = 256;  // per chain: S [0,128) (P over its first 64 columns), then O [128,256)
 constexpr uint32_t kColO = 128;
 constexpr float kLazy = 8.f;
+#ifndef BRK_POLY_OF_8
+#define BRK_POLY_OF_8 4
+#endif
+constexpr int kPolyOf8 = BRK_POLY_OF_8;  // exponentials per 8 evaluated as a polynomial on the FMA pipe: 0, 2 or 4
 constexpr uint32_t kWaitBudget = 1u << 18;
+constexpr int kTileFixedCost = 136;  // cost of a row tile beyond its keys (output drain), in keys
 
 enum {
   kQFull = 0,    // +chain  TMA -> MMA: Q tile landed
@@ -116,7 +121,7 @@ enum {
   kJobFree = kJobFull + 2 * kJobRing,     // +chain*kJobRing+i  MMA warp + 4 softmax warps -> TMA warp (5 arrivals)
   kNumBars = kJobFree + 2 * kJobRing
 };
-static_assert(kNumBars * 8 + 4 <= 512, "barrier area");
+static_assert(kNumBars * 8 + 16 <= 512, "barrier area");  // + the TMEM base address and the tensor-pipe token
 
 // Division by a run-time constant with a host-computed reciprocal (round-up method, exact for every
 // 32-bit numerator): q = umulhi(n, mul); n / d = (((n - q) >> 1) + q) >> shift.
@@ -152,7 +157,8 @@ struct TcArgs {
   int n_split;      // key chunks of the query block's context (1 = no split)
   int lq_max;       // rows per (prompt, head) in the partial buffers (bound on the query block's length)
   int pairs_q;      // row-tile pairs of the query block (covers lq_max)
-  int n_groups;     // groups of kGroup blocks among blocks 0 .. M-2
+  int group;        // consecutive blocks 0 .. M-2 of one (prompt, KV head) per work item (their prefix stays resident)
+  int n_groups;     // such groups per (prompt, KV head)
   int o_align32;    // output rows are 32-byte aligned (enables 32-byte stores)
   int sec1, total_items;
   FastDiv div_sec1, div_nbg, div_nk;  // by nbg*n_split, nbg, Nk
@@ -248,8 +254,8 @@ __device__ __forceinline__ ItemRaw load_item(const TcArgs& a, int idx, int lane)
     const int i2 = idx - a.sec1;
     const int grp = (int)fdiv((uint32_t)i2, a.div_nbg);
     bg = i2 - grp * nbg;
-    r.m = grp * kGroup;
-    r.cnt = min(kGroup, a.M - 1 - r.m);
+    r.m = grp * a.group;
+    r.cnt = min(a.group, a.M - 1 - r.m);
     r.p = r.chunk = 0;
   }
   r.b = (int)fdiv((uint32_t)bg, a.div_nk);
@@ -326,10 +332,9 @@ __device__ __forceinline__ Pair decode_pair(const TcArgs& a, int b, int g, int m
   return pr;
 }
 
-// chain of the i-th largest row tile of a resident block (tiles are dealt 0,1,1,0,0,1,1,0,...) and the
-// position of the same chain's next tile
+// chain of the i-th largest row tile of a resident block when there are too many tiles to try every split
+// (tiles are dealt 0,1,1,0,0,1,1,0,...)
 __device__ __forceinline__ int deal_chain(int i) { return ((i & 3) == 0 || (i & 3) == 3) ? 0 : 1; }
-__device__ __forceinline__ int deal_next(int i) { return ((i & 3) == 0 || (i & 3) == 2) ? i + 3 : i + 1; }
 
 __global__ void __launch_bounds__(kThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -361,6 +366,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* smem = smem_raw + (sbase - raw);
   const uint32_t sBar = sbase + kOffBar;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + kNumBars * 8);
+  int* const pipe_token = reinterpret_cast<int*>(smem + kOffBar + kNumBars * 8 + 8);
   auto bar = [&](int i) { return sBar + (uint32_t)i * 8u; };
 
   bool failed = false;
@@ -372,6 +378,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (i >= kJobFree) cnt = 5u;                                                        // MMA warp + four softmax warps
       ptx::mbar_init(bar(i), cnt);
     }
+    *pipe_token = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmQ);
     ptx::prefetch_tmap(&tmK);
@@ -413,19 +420,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // The whole warp runs the control flow (so addresses and counters stay warp-uniform); one lane
     // issues the copies.
     const bool leader = lane == 0;
-    uint32_t n_pub[2] = {0, 0}, q_loads[2] = {0, 0};
+    uint32_t n_pub0 = 0, n_pub1 = 0;
     uint32_t out_mask = 0;    // bit s: a load signalled on barrier kKVFull+s has not been handed back yet
     uint32_t free_par = 0;    // bit s: parity of the next kKVFree+s phase
     uint32_t stream_tiles = 0;
     int mode = 0;             // 1 streamed, 2 resident: the two use the slots' barriers differently
     auto publish = [&](int x, const Job& it) {
-      const uint32_t slot = n_pub[x] % kJobRing;
-      if (n_pub[x] >= kJobRing) wait(kJobFree + x * kJobRing + slot, n_pub[x] / kJobRing - 1, 14 + x);
+      const uint32_t np = x ? n_pub1 : n_pub0;
+      const uint32_t slot = np % kJobRing;
+      if (np >= kJobRing) wait(kJobFree + x * kJobRing + slot, np / kJobRing - 1, 14 + x);
       if (leader) {
         write_record(job_ring + (x * kJobRing + slot) * 16, it);
         ptx::mbar_arrive(bar(kJobFull + x * kJobRing + slot));  // release: the record is visible to whoever sees the phase flip
       }
-      ++n_pub[x];
+      if (x) ++n_pub1; else ++n_pub0;
     };
     // wait until both MMA warps have handed back the load last signalled on barrier s
     auto drain = [&](int s) {
@@ -437,20 +445,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     };
     auto set_mode = [&](int m) {
       if (mode != m) {
-#pragma unroll
+#pragma unroll 1
         for (int s = 0; s < kSlots; ++s) drain(s);
         mode = m;
       }
-    };
-    auto load_q = [&](int x, int g, int b, int tok) {
-      if (q_loads[x] > 0) wait(kQFree + x, q_loads[x] - 1, 10 + x);
-      const uint32_t dst = sbase + kOffQ + (uint32_t)x * kQBytes;
-      if (leader) {
-        ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
-        ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, g * G, tok, b);
-        ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, g * G, tok, b);
-      }
-      ++q_loads[x];
     };
     // K and V of 64 keys starting at token slot `lo` -> pool slot s, completion on barrier `bs`
     auto load_slot = [&](int s, int bs, int g, int b, int lo) {
@@ -482,8 +480,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish(0, it);
       it.t0 = pr.t0_1; it.n = pr.n_1;
       publish(1, it);
-      if (pr.n_0 > 0) load_q(0, g, b, start + pr.t0_0);
-      if (pr.n_1 > 0) load_q(1, g, b, start + pr.t0_1);
       for (int t = 0; t < T; ++t) {
         const int tb = (int)((stream_tiles + (uint32_t)t) & 1u);
         drain(2 * tb);
@@ -510,41 +506,80 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const int R = (len + TOK - 1) / TOK;
       const int n_keep = keep_out ? (m > 0 ? n_ctx : (l0 + BN - 1) / BN) : 0;
       set_mode(2);
-      for (int s = ns_blk - 1; s >= (keep_in ? n_ctx : 0); --s) {
-        drain(s);
-        const int lo = s < n_ctx ? s0 + s * BN : start + (s - n_ctx) * BN;
-        if (leader) {
-          ptx::mbar_expect_tx(bar(kKVFull + s), kSlotBytes);
-          load_slot(s, s, g, b, lo);
+      // K/V slots, highest first (the previous block hands them back in that order).  The loop stops at the first
+      // slot that is still in use; the block's jobs are published before the producer sleeps on it, so that the
+      // chains find their records and request their Q tiles meanwhile (their MMA warps wait for the slots).
+      const int s_lo = keep_in ? n_ctx : 0;
+      int s_next = ns_blk - 1;
+      auto load_slots = [&](bool blocking) {
+        for (; s_next >= s_lo; --s_next) {
+          const int s = s_next;
+          if ((out_mask >> s) & 1u) {
+            if (!blocking && !__all_sync(0xffffffffu, ptx::mbar_test(bar(kKVFree + s), (free_par >> s) & 1u))) return;
+            drain(s);
+          }
+          const int lo = s < n_ctx ? s0 + s * BN : start + (s - n_ctx) * BN;
+          if (leader) {
+            ptx::mbar_expect_tx(bar(kKVFull + s), kSlotBytes);
+            load_slot(s, s, g, b, lo);
+          }
+          out_mask |= 1u << s;
         }
-        out_mask |= 1u << s;
-      }
+      };
+      load_slots(false);
       Job it;
       it.b = b; it.g = g; it.m = m; it.chunk = 0;
       it.start = start; it.len = len;
       it.ctx_lo = s0; it.ctx_hi = s0 + ctx; it.n_ctx = n_ctx; it.j0 = 0;
       it.tile0 = 0;
       auto slots_of = [&](int i) { return n_ctx + (min(len, (R - i) * TOK) + BN - 1) / BN; };  // i-th largest tile
+      // Deal the row tiles (largest first) to the two chains so that the chains finish together: a tile costs
+      // its keys plus a fixed share for writing the output.  Up to 11 tiles every split is tried (the lanes
+      // share the 2^(R-1) candidates); beyond that the tiles are dealt 0,1,1,0,0,1,1,0,...
+      uint32_t cmask = 0;  // bit i: chain of the i-th largest tile
+      if (R <= 11) {
+        const int n_cand = 1 << (R - 1);  // tile 0 (the largest) goes to chain 0
+        uint32_t best = 0xffffffffu;
+        for (int c = lane; c < n_cand; c += 32) {
+          int load0 = 0, load1 = 0;
+          for (int i = 0; i < R; ++i) {
+            const int cost = ctx + min(len, (R - i) * TOK) + kTileFixedCost;
+            if (((c << 1) >> i) & 1) load1 += cost; else load0 += cost;
+          }
+          best = min(best, ((uint32_t)max(load0, load1) << 11) | (uint32_t)(c << 1));
+        }
+        cmask = __reduce_min_sync(0xffffffffu, best) & 0x7ffu;
+      } else {
+        for (int i = 0; i < R; ++i) cmask |= (uint32_t)deal_chain(i) << i;
+      }
+      auto next_same = [&](int i) {  // position of the same chain's next tile, or R
+        const uint32_t same = (((cmask >> i) & 1u) ? cmask : ~cmask) & ~((2u << i) - 1u) & ((1u << R) - 1u);
+        return same ? __ffs((int)same) - 1 : R;
+      };
+      const int first1 = (cmask & ((1u << R) - 1u)) ? __ffs((int)cmask) - 1 : R;  // chain 1's first tile (R: none)
       for (int i = 0; i < R; ++i) {
-        const int x = deal_chain(i), r = R - 1 - i;
+        const int x = (int)((cmask >> i) & 1u), r = R - 1 - i;
         it.t0 = r * TOK;
         it.own_n = min(len, it.t0 + TOK);
         it.n = slots_of(i);
-        const bool first = i < 2;
-        const int nx = deal_next(i);
+        const bool first = i == 0 || i == first1;
+        const int nx = next_same(i);
         const int rel_lo = max(n_keep, nx < R ? slots_of(nx) : 0);  // slots kept for the next block are never handed back
         const int rel_hi = first ? ns_blk : it.n;
         it.flags = kFDoc | (first ? kFFirst : 0) | (keep_in ? kFKeep : 0);
         it.aux = rel_lo | (rel_hi << 8);
         publish(x, it);
-        load_q(x, g, b, start + it.t0);
+        // Only the two largest tiles are published ahead of the slots that are still busy: a ring that filled
+        // up with jobs whose K/V cannot be loaded (because the producer sleeps on the ring) would never drain.
+        if (i == 1) load_slots(true);
       }
-      if (R == 1) {  // chain 1 has no row tile: it only hands the slots back
+      if (first1 == R) {  // chain 1 has no row tile: it only hands the slots back
         it.t0 = 0; it.own_n = 0; it.n = 0;
         it.flags = kFDoc | kFFirst | (keep_in ? kFKeep : 0);
         it.aux = n_keep | (ns_blk << 8);
         publish(1, it);
       }
+      load_slots(true);
     };
 
     // The work list is handed out dynamically: whichever CTA is free claims the next index.  Claims
@@ -611,6 +646,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait(kKVFull + s, (full_par >> s) & 1u, 22 + x);
       full_par ^= 1u << s;
     };
+    // The tensor pipe executes MMAs in the order they were issued, whoever issued them.  A chain's P V and
+    // next Q K^T are issued under a token, so the two chains' groups do not interleave: the chain that asks
+    // first gets its S tile back after ONE group instead of two, which keeps the chains half a round apart
+    // (one in its softmax while the other's MMAs run) instead of in lock step.
+    auto pipe_acquire = [&]() {
+      if (leader) {
+        uint32_t spins = 0;
+        while (atomicCAS(pipe_token, 0, 1) != 0 && ++spins < kWaitBudget) {}  // a spin that runs out just goes ahead
+      }
+      __syncwarp();
+    };
+    auto pipe_release = [&]() {
+      __syncwarp();
+      if (leader) atomicExch(pipe_token, 0);
+    };
     // S = Q K^T against `keys` keys starting at pool slot `slot`
     auto issue_qk = [&](int slot, int keys, bool last) {
       const uint32_t idesc = idesc_qk0 | ((uint32_t)((keys + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
@@ -640,21 +690,54 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ptx::mma_commit(bar(kPVDone + x));
       }
     };
+    // keys of a job's last 128-key tile (every earlier tile spans 128 keys: a short context slot inside a
+    // tile is masked by the softmax, not trimmed)
+    auto last_tile_keys = [&](const Job& jb) {
+      const int Tj = (jb.n + 1) >> 1;
+      if (Tj == 0) return 0;
+      const int cnt = min(2, jb.n - 2 * (Tj - 1));
+      int nk, own_off; bool own;
+      tile_lo(jb, 2 * (Tj - 1) + cnt - 1, nk, own, own_off);
+      return (cnt - 1) * BN + nk;
+    };
+    // This warp also loads its chain's Q tiles: it is the one that knows when the buffer is free (the job's last
+    // Q K^T has completed) and it has nothing else to do at that moment.  q_issued counts the tiles requested;
+    // the next job's tile is requested as soon as the current job's last Q K^T is in the pipe and its record
+    // has been published, otherwise at the start of that job.
+    uint32_t q_issued = 0;
+    auto request_q = [&](const Job& jb) {
+      if (q_issued > 0) wait(kQFree + x, q_issued - 1, 28 + x);  // every Q K^T of the previous job has read the buffer
+      if (leader) {
+        const uint32_t dst = sbase + kOffQ + (uint32_t)x * kQBytes;
+        ptx::mbar_expect_tx(bar(kQFull + x), kQBytes);
+        ptx::tma_load_4d(dst, &tmQ, bar(kQFull + x), 0, jb.g * G, jb.start + jb.t0, jb.b);
+        ptx::tma_load_4d(dst + BM * 128, &tmQ, bar(kQFull + x), 64, jb.g * G, jb.start + jb.t0, jb.b);
+      }
+      ++q_issued;
+    };
+    // called once the current job's last Q K^T has been issued: request the next job's Q tile if its record is there
+    auto request_next_q = [&](uint32_t job_no) {
+      if (q_issued != q_uses) return;  // already requested
+      const uint32_t nslot = (job_no + 1) % kJobRing;
+      if (!__all_sync(0xffffffffu, ptx::mbar_test(bar(kJobFull + x * kJobRing + nslot), ((job_no + 1) / kJobRing) & 1u))) return;
+      const Job nxt = read_record(job_ring + (x * kJobRing + nslot) * 16);
+      if (!(nxt.flags & kFStop) && nxt.n > 0) request_q(nxt);
+    };
+    bool pre_qk = false;  // the first Q K^T of the job fetched next is already in the pipe
     for (uint32_t job_no = 0;; ++job_no) {
       const Job it = next_job(x, job_no);
       if (it.flags & kFStop) break;
       const int n = it.n, T = (n + 1) >> 1;
-      // Every tile but the last spans 128 keys (a short context slot inside a tile is masked by the
-      // softmax, not trimmed); the last one is computed once here, off the per-tile path.
-      int last_keys = 0;
-      if (T > 0) {
-        const int cnt = min(2, n - 2 * (T - 1));
-        int nk, own_off; bool own;
-        tile_lo(it, 2 * (T - 1) + cnt - 1, nk, own, own_off);
-        last_keys = (cnt - 1) * BN + nk;
-      }
+      const int last_keys = last_tile_keys(it);
       auto keys_of = [&](int t) { return t + 1 < T ? BT : last_keys; };
-      if (T > 0) { wait(kQFull + x, q_uses, 20 + x); ++q_uses; }
+      // (a job whose first Q K^T was issued ahead has had its Q phase consumed there: by now the barrier may be
+      // a phase further, and a parity wait must never fall two phases behind)
+      if (T > 0 && !pre_qk) {
+        if (q_issued == q_uses) request_q(it);  // not requested ahead
+        wait(kQFull + x, q_uses, 20 + x);
+        ++q_uses;
+      }
+      if (T == 1 && pre_qk) request_next_q(job_no);  // its only Q K^T went out with the previous job's last P V
       if (it.flags & kFDoc) {
         // ---- resident block: tile t = pool slots 2t, 2t+1; slots land once per block ----
         if (it.flags & kFFirst) blk_waited = (it.flags & kFKeep) ? it.n_ctx : 0;
@@ -662,21 +745,47 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           while (blk_waited < ns) { wait_full(blk_waited); ++blk_waited; }
         };
         if (T > 0) {
-          ensure(min(n, 2));
-          ptx::tc_fence_after_sync();
-          issue_qk(0, keys_of(0), T == 1);
+          if (!pre_qk) {
+            ensure(min(n, 2));
+            pipe_acquire();
+            ptx::tc_fence_after_sync();
+            issue_qk(0, keys_of(0), T == 1);
+            pipe_release();
+            if (T == 1) request_next_q(job_no);
+          }
+          pre_qk = false;
           for (int t = 0; t < T; ++t) {
+            if (t + 1 < T) ensure(min(n, 2 * t + 4));
             wait(kPFull + x, p_seen, 24 + x);
             ++p_seen;
             if (t == 0 && jobs_done > 0) wait(kOFree + x, jobs_done - 1, 26 + x);
+            // After the job's last tile the chain's next row tile of the same block can start at once if its
+            // record and its Q tile are already here (its first key tile is resident): its first Q K^T then
+            // rides behind this P V, and its S tile is waiting when the softmax warps have drained O.
+            Job nxt{};
+            bool chain_on = false;
+            if (t + 1 == T) {
+              const uint32_t nslot = (job_no + 1) % kJobRing;
+              if (__all_sync(0xffffffffu, ptx::mbar_test(bar(kJobFull + x * kJobRing + nslot), ((job_no + 1) / kJobRing) & 1u))) {
+                nxt = read_record(job_ring + (x * kJobRing + nslot) * 16);
+                chain_on = (nxt.flags & kFDoc) && !(nxt.flags & (kFFirst | kFStop)) && nxt.n > 0 &&
+                           blk_waited >= min(nxt.n, 2) && q_issued > q_uses &&
+                           __all_sync(0xffffffffu, ptx::mbar_test(bar(kQFull + x), q_uses & 1u));
+              }
+            }
+            pipe_acquire();
             ptx::tc_fence_after_sync();
             issue_pv(2 * t, keys_of(t), t == 0);
-            if (t + 1 < T) {
-              // the chain's next S tile: queued behind the P V that reads P out of the same columns
-              ensure(min(n, 2 * t + 4));
-              ptx::tc_fence_after_sync();
-              issue_qk(2 * t + 2, keys_of(t + 1), t + 2 == T);
+            // the chain's next S tile: queued behind the P V that reads P out of the same columns
+            if (t + 1 < T) issue_qk(2 * t + 2, keys_of(t + 1), t + 2 == T);
+            if (chain_on) {
+              const int Tn = (nxt.n + 1) >> 1;
+              issue_qk(0, Tn > 1 ? BT : last_tile_keys(nxt), Tn == 1);
+              pre_qk = true;
+              ++q_uses;  // its Q tile has landed (tested above): that phase is consumed here
             }
+            pipe_release();
+            if (t + 2 == T) request_next_q(job_no);  // the job's last Q K^T is in the pipe
           }
           ++jobs_done;
         }
@@ -698,25 +807,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         };
         if (T > 0) {
           need_kv(0);
+          pipe_acquire();
           ptx::tc_fence_after_sync();
           issue_qk(2 * (it.tile0 & 1), keys_of(0), T == 1);
+          pipe_release();
+          if (T == 1) request_next_q(job_no);
         }
         for (int t = 0; t < Ti; ++t) {
           const int slot = 2 * ((it.tile0 + t) & 1);
           if (t < T) {
+            if (t + 1 < T) need_kv(t + 1);  // (its ring position was handed back after P V of tile t-1)
             wait(kPFull + x, p_seen, 24 + x);
             ++p_seen;
             if (t == 0 && jobs_done > 0) wait(kOFree + x, jobs_done - 1, 26 + x);
+            pipe_acquire();
             ptx::tc_fence_after_sync();
             issue_pv(slot, keys_of(t), t == 0);
+            if (leader) ptx::mma_commit(bar(kKVFree + slot));
+            if (t + 1 < T) issue_qk(2 * ((it.tile0 + t + 1) & 1), keys_of(t + 1), t + 2 == T);
+            pipe_release();
+            if (t + 2 == T) request_next_q(job_no);  // the job's last Q K^T is in the pipe
           } else {
             need_kv(t);  // not visible to this chain: consume the phase, then hand the tile back
-          }
-          if (leader) ptx::mma_commit(bar(kKVFree + slot));
-          if (t + 1 < T) {
-            need_kv(t + 1);
-            ptx::tc_fence_after_sync();
-            issue_qk(2 * ((it.tile0 + t + 1) & 1), keys_of(t + 1), t + 2 == T);
+            if (leader) ptx::mma_commit(bar(kKVFree + slot));
           }
         }
         if (T > 0) ++jobs_done;
@@ -868,17 +981,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                   float t0, t1, p2, p3;
                   ptx::unpack2(t01, t0, t1);
                   const float p0 = ptx::ex2(t0), p1 = ptx::ex2(t1);
-                  const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
-                  ptx::unpack2(p23, p2, p3);
-                  if (kGrouped && c0 + 8 > lim_lo) {
-                    // a masked column must contribute exactly nothing: the polynomial maps -inf to 2^-126,
-                    // which times a huge (finite) value in a padding slot of V would still be visible
-                    p2 = sr[c + 2] == 0xff800000u ? 0.f : p2;
-                    p3 = sr[c + 3] == 0xff800000u ? 0.f : p3;
-                    ps2[1] = ptx::add2(ps2[1], ptx::pack2(p2, p3));
+                  // kPolyOf8 of every 8 exponentials go to the FMA pipe as a polynomial, the rest to the
+                  // special-function unit (a -inf logit gives exactly 0 there)
+                  if ((kPolyOf8 == 4) || (kPolyOf8 == 2 && (c & 4))) {
+                    const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
+                    ptx::unpack2(p23, p2, p3);
+                    if (kGrouped && c0 + 8 > lim_lo) {
+                      // a masked column must contribute exactly nothing: the polynomial maps -inf to 2^-126,
+                      // which times a huge (finite) value in a padding slot of V would still be visible
+                      p2 = sr[c + 2] == 0xff800000u ? 0.f : p2;
+                      p3 = sr[c + 3] == 0xff800000u ? 0.f : p3;
+                    }
                   } else {
-                    ps2[1] = ptx::add2(ps2[1], p23);
+                    float t2, t3;
+                    ptx::unpack2(t23, t2, t3);
+                    p2 = ptx::ex2(t2);
+                    p3 = ptx::ex2(t3);
                   }
+                  ps2[1] = ptx::add2(ps2[1], ptx::pack2(p2, p3));
                   ps2[0] = ptx::add2(ps2[0], ptx::pack2(p0, p1));
                   __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
                   pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
@@ -1114,11 +1234,7 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   const int TOK = BM / G;
   const int lq = query_rows(p);
   const int pairs_q = (lq + 2 * TOK - 1) / (2 * TOK);
-  const int n_groups = p.M > 1 ? (p.M - 1 + kGroup - 1) / kGroup : 0;
   const int64_t nbg = (int64_t)p.B * p.Nk;
-  const int64_t sec1 = nbg * ns * pairs_q;
-  const int64_t total_items = sec1 + nbg * n_groups;
-  BRK_REQUIRE(total_items < (1ll << 30), BRK_E_UNSUPPORTED, "too many work items (%lld)", (long long)total_items);
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_tmap_bf16(&tq, p.q.ptr, HD, p.N, p.S, p.B, p.q.stride_h, p.q.stride_s, p.q.stride_b, G, TOK))) return rc;
@@ -1135,6 +1251,15 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
     BRK_REQUIRE(sms[dev] > 0, BRK_E_CUDA, "could not read the SM count");
     configured[dev] = true;
   }
+  // Blocks are handed out in groups of consecutive blocks of one (prompt, KV head), so that the prefix's K/V
+  // stays in shared memory from one block to the next; the groups shrink when there are too few blocks to
+  // keep every SM busy for several rounds.
+  int group = (int)((nbg * (p.M > 1 ? p.M - 1 : 0)) / (6 * (int64_t)sms[dev]));
+  group = group < 1 ? 1 : (group > kMaxGroup ? kMaxGroup : group);
+  const int n_groups = p.M > 1 ? (p.M - 1 + group - 1) / group : 0;
+  const int64_t sec1 = nbg * ns * pairs_q;
+  const int64_t total_items = sec1 + nbg * n_groups;
+  BRK_REQUIRE(total_items < (1ll << 30), BRK_E_UNSUPPORTED, "too many work items (%lld)", (long long)total_items);
   TcArgs a;
   a.o = make_view(p.o);
   a.lse = p.lse;
@@ -1148,6 +1273,7 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
   a.n_split = ns;
   a.lq_max = lq;
   a.pairs_q = pairs_q;
+  a.group = group;
   a.n_groups = n_groups;
   a.o_align32 = (((uintptr_t)p.o.ptr & 31) == 0 && p.o.stride_b % 16 == 0 && p.o.stride_h % 16 == 0 && p.o.stride_s % 16 == 0) ? 1 : 0;
   a.sec1 = (int)sec1;

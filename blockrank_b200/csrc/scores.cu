@@ -36,7 +36,8 @@ struct ScoreArgs {
   const int32_t* blk_start;
   const int32_t* blk_len;
   float2* partial;  // [B, N, R, nd]
-  unsigned* done;   // [B] CTAs of the prompt that have published their partials; wraps to 0 by itself
+  unsigned* done_bg;  // [B, Nk] document CTAs of the (prompt, KV head) that have published their partials
+  unsigned* done_b;   // [B] KV-head groups of the prompt whose masses are written; both wrap to 0 by themselves
   float* mass;      // [B, N, R, nd] out
   float* logits;    // [B, nd] out, optional
   float inv_count_temp;  // 1 / (N * R * temperature)
@@ -51,52 +52,79 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2)
   m = mn;
 }
 
-// Called by every thread of a partial-kernel CTA after its (max, sum) pairs are written.  The CTA that
-// completes prompt b -- the last of its (documents x KV heads) CTAs to bump the prompt's counter -- finalizes
-// it.  Phase 1, one warp per (head, signal row) at a time: merge the per-document pairs into the softmax over
-// all document tokens and emit the per-document probability mass.  Phase 2 (when logits are wanted), one
-// thread per document: mean over heads and rows of the masses just written, divided by the temperature,
-// summed in a fixed order.  atomicInc wraps the counter back to 0, so the scratch is ready for the next call.
-__device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b) {
+// Called by every thread of a partial-kernel CTA after its (max, sum) pairs are written.  Two levels of
+// "last one finishes the job", each a counter that atomicInc wraps back to 0 (so the scratch is ready for the
+// next call): the last of the nd document CTAs of a (prompt, KV head) merges the per-document pairs of that
+// group's G*R (head, signal row) rows into the softmax over all document tokens and writes their per-document
+// probability masses; the last of the Nk groups of a prompt then writes the prompt's logits -- the mean over
+// heads and rows of the masses, divided by the temperature, summed in a fixed order.
+__device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int g) {
   __shared__ int is_last;
+  const int nd = a.M - 2;
   __syncthreads();  // every partial of this CTA has been issued
   if (threadIdx.x == 0) {
     __threadfence();  // ... and is visible device-wide before the counter moves
-    const unsigned total = (unsigned)(a.M - 2) * (unsigned)a.Nk;
-    is_last = atomicInc(a.done + b, total - 1) == total - 1;
+    is_last = atomicInc(a.done_bg + b * a.Nk + g, (unsigned)nd - 1) == (unsigned)nd - 1;
   }
   __syncthreads();
   if (!is_last) return;
   __threadfence();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int NR = a.N * a.R, nd = a.M - 2;
-  for (int row = warp; row < NR; row += nwarps) {
-    const size_t w = (size_t)b * NR + row;
+  const int G = a.N / a.Nk, GR = G * a.R;
+  constexpr int kHeld = 8;  // pairs per lane kept in registers: one round trip per row up to 256 documents
+  for (int row = warp; row < GR; row += nwarps) {
+    const size_t w = ((size_t)b * a.N + (size_t)g * G) * a.R + row;  // (head g*G + row / R, signal row row % R)
     const float2* p = a.partial + w * nd;
+    float2 held[kHeld];
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int d = lane + 32 * i;
+      held[i] = d < nd ? __ldcg(&p[d]) : make_float2(-INFINITY, 0.f);
+    }
     float mx = -INFINITY;
-    for (int d = lane; d < nd; d += 32) mx = fmaxf(mx, __ldcg(&p[d]).x);
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) mx = fmaxf(mx, held[i].x);
+    for (int d = lane + 32 * kHeld; d < nd; d += 32) mx = fmaxf(mx, __ldcg(&p[d]).x);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     const float ref = (mx == -INFINITY) ? 0.f : mx;
     float z = 0.f;
-    for (int d = lane; d < nd; d += 32) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      held[i].y *= exp2f(held[i].x - ref);  // un-normalised mass of the document
+      z += held[i].y;
+    }
+    for (int d = lane + 32 * kHeld; d < nd; d += 32) {
       const float2 x = __ldcg(&p[d]);
       z += x.y * exp2f(x.x - ref);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) z += __shfl_xor_sync(0xffffffffu, z, off);
     const float inv = z > 0.f ? 1.f / z : 0.f;
-    for (int d = lane; d < nd; d += 32) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      const int d = lane + 32 * i;
+      if (d < nd) a.mass[w * nd + d] = held[i].y * inv;
+    }
+    for (int d = lane + 32 * kHeld; d < nd; d += 32) {
       const float2 x = __ldcg(&p[d]);
       a.mass[w * nd + d] = x.y * exp2f(x.x - ref) * inv;
     }
   }
   if (a.logits == nullptr) return;
-  __syncthreads();  // the masses of this prompt, written by this CTA, are visible to all its threads
+  __syncthreads();  // this group's masses have been issued
+  if (threadIdx.x == 0) {
+    __threadfence();
+    is_last = atomicInc(a.done_b + b, (unsigned)a.Nk - 1) == (unsigned)a.Nk - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int NR = a.N * a.R;
   for (int d = threadIdx.x; d < nd; d += blockDim.x) {
     const float* p = a.mass + (size_t)b * NR * nd + d;
     float acc = 0.f;
-    for (int i = 0; i < NR; ++i) acc += p[(size_t)i * nd];
+    for (int i = 0; i < NR; ++i) acc += __ldcg(&p[(size_t)i * nd]);
     a.logits[(size_t)b * nd + d] = acc * a.inv_count_temp;
   }
 }
@@ -213,7 +241,7 @@ __global__ void __launch_bounds__(kThreads) doc_partial_kernel(ScoreArgs a) {
       a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
     }
   }
-  finalize_if_last(a, b);
+  finalize_if_last(a, b, g);
 }
 
 __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -316,7 +344,7 @@ __global__ void __launch_bounds__(kThreads) doc_partial_mma_kernel(ScoreArgs a) 
       a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
     }
   }
-  finalize_if_last(a, b);
+  finalize_if_last(a, b, g);
 }
 
 // block index of a slot, or -1 for padding (blk_start is non-decreasing)
@@ -381,7 +409,8 @@ ScoreArgs make_args(const brk_score_params& p) {
   a.blk_start = p.blk_start;
   a.blk_len = p.blk_len;
   a.partial = nullptr;
-  a.done = nullptr;
+  a.done_bg = nullptr;
+  a.done_b = nullptr;
   a.mass = nullptr;
   a.logits = nullptr;
   a.inv_count_temp = 0.f;
@@ -408,32 +437,36 @@ int check(const brk_score_params& p) {
 
 }  // namespace
 
-// scratch layout: [B, N, R, nd] (max, sum) pairs, then B per-prompt completion counters
+// scratch layout: completion counters ([B, Nk] then [B] unsigned, padded to `counter_bytes`), then the
+// [B, N, R, nd] (max, sum) pairs
+static size_t counter_bytes(const brk_score_params& p) {
+  return (((size_t)(p.B > 0 ? p.B : 0) * (size_t)(p.Nk + 1) * sizeof(unsigned)) + 255) & ~(size_t)255;
+}
 static size_t partial_bytes(const brk_score_params& p) {
   const size_t nd = p.M > 2 ? p.M - 2 : 0;
   return (size_t)p.B * p.N * p.R * nd * sizeof(float2);
 }
 
-size_t doc_scores_workspace(const brk_score_params& p) {
-  return partial_bytes(p) + (((size_t)(p.B > 0 ? p.B : 0) * sizeof(unsigned) + 15) & ~(size_t)15);
-}
+size_t doc_scores_workspace(const brk_score_params& p) { return counter_bytes(p) + partial_bytes(p); }
 
 // counters_zero: the caller guarantees that the counters are zero (they return to zero after every completed call)
-static int doc_scores_run(const brk_score_params& p, void* ws, size_t ws_bytes, bool counters_zero, cudaStream_t st) {
+static int doc_scores_run(const brk_score_params& p, void* ws, size_t ws_bytes, size_t counter_region, bool counters_zero,
+                          cudaStream_t st) {
   int rc = check(p);
   if (rc) return rc;
   BRK_REQUIRE(p.M >= 3, BRK_E_ARG, "document scores need at least one document block (M=%d)", p.M);
   BRK_REQUIRE(p.rows && p.doc_mass, BRK_E_ARG, "rows / doc_mass must be given");
-  BRK_REQUIRE(ws != nullptr && ws_bytes >= doc_scores_workspace(p) && ((uintptr_t)ws & 7) == 0, BRK_E_WORKSPACE,
-              "workspace %zu < %zu bytes (or not 8-byte aligned)", ws_bytes, doc_scores_workspace(p));
+  BRK_REQUIRE(ws != nullptr && ws_bytes >= counter_region + partial_bytes(p) && ((uintptr_t)ws & 7) == 0, BRK_E_WORKSPACE,
+              "workspace %zu < %zu bytes (or not 8-byte aligned)", ws_bytes, counter_region + partial_bytes(p));
   BRK_REQUIRE(p.temperature > 0.f, BRK_E_ARG, "temperature must be positive");
   ScoreArgs a = make_args(p);
-  a.partial = reinterpret_cast<float2*>(ws);
-  a.done = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(ws) + partial_bytes(p));
+  a.done_bg = reinterpret_cast<unsigned*>(ws);
+  a.done_b = a.done_bg + (size_t)p.B * p.Nk;
+  a.partial = reinterpret_cast<float2*>(static_cast<unsigned char*>(ws) + counter_region);
   a.mass = p.doc_mass;
   a.logits = p.logits;
   a.inv_count_temp = 1.f / ((float)(p.N * p.R) * p.temperature);
-  if (!counters_zero) BRK_CUDA(cudaMemsetAsync(a.done, 0, (size_t)p.B * sizeof(unsigned), st));
+  if (!counters_zero) BRK_CUDA(cudaMemsetAsync(ws, 0, (size_t)p.B * (p.Nk + 1) * sizeof(unsigned), st));
   const int nd = p.M - 2, G = p.N / p.Nk;
   dim3 grid(nd, p.B * p.Nk);
   const size_t pitch = (size_t)p.D * (p.dtype == BRK_BF16 ? 2 : 4) + 16;
@@ -454,7 +487,7 @@ static int doc_scores_run(const brk_score_params& p, void* ws, size_t ws_bytes, 
 }
 
 int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
-  return doc_scores_run(p, ws, ws_bytes, false, st);
+  return doc_scores_run(p, ws, ws_bytes, counter_bytes(p), false, st);
 }
 
 // ---- allocation-free variant ----------------------------------------------------------------
@@ -463,14 +496,20 @@ int doc_scores_launch(const brk_score_params& p, void* ws, size_t ws_bytes, cuda
 // loads the library holds these bytes until the process exits.  The image initialises it to zero, and
 // the counters wrap back to zero at the end of every completed call, so nothing is cleared per call.
 static __device__ __align__(256) unsigned char g_static_scratch[BRK_STATIC_SCRATCH_BYTES];
+constexpr size_t kStaticCounterBytes = 16384;  // room for 4096 counters: B * (Nk + 1) <= 4096
 
 int doc_scores_static_launch(const brk_score_params& p, cudaStream_t st) {
   int rc = check(p);  // argument errors are reported as such, before the size test
   if (rc) return rc;
   BRK_REQUIRE(p.M >= 3, BRK_E_ARG, "document scores need at least one document block (M=%d)", p.M);
-  const size_t need = doc_scores_workspace(p);
+  // the counters keep a fixed place at the front of the array whatever the problem size, so that the zeros
+  // they return to after one call are the zeros the next call starts from
+  BRK_REQUIRE(counter_bytes(p) <= kStaticCounterBytes, BRK_E_WORKSPACE,
+              "brk_doc_scores_static: B*(Nk+1) = %d completion counters, the built-in array reserves room for %zu",
+              p.B * (p.Nk + 1), kStaticCounterBytes / sizeof(unsigned));
+  const size_t need = kStaticCounterBytes + partial_bytes(p);
   BRK_REQUIRE(need <= (size_t)BRK_STATIC_SCRATCH_BYTES, BRK_E_WORKSPACE,
-              "brk_doc_scores_static: B*N*R*(M-2)*8 + 4*B = %zu bytes of scratch needed, the built-in array holds %zu; "
+              "brk_doc_scores_static: 16384 + B*N*R*(M-2)*8 = %zu bytes of scratch needed, the built-in array holds %zu; "
               "use brk_doc_scores with a caller workspace for this size",
               need, (size_t)BRK_STATIC_SCRATCH_BYTES);
   // In host code the array's name is only a handle; the kernels need its device address, which
@@ -489,7 +528,7 @@ int doc_scores_static_launch(const brk_score_params& p, cudaStream_t st) {
   }
   // every (prompt, head, row, document) pair is overwritten by the partial kernels before the finalizing CTA
   // reads it, and the counters are back at zero, so nothing left by an earlier call has to be cleared
-  return doc_scores_run(p, ptr, (size_t)BRK_STATIC_SCRATCH_BYTES, true, st);
+  return doc_scores_run(p, ptr, (size_t)BRK_STATIC_SCRATCH_BYTES, kStaticCounterBytes, true, st);
 }
 
 int raw_scores_launch(const brk_score_params& p, void* out, cudaStream_t st) {

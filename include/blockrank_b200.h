@@ -173,8 +173,8 @@ BRK_API int brk_doc_scores(const brk_score_params* p, void* workspace, size_t wo
  * output buffers it was given.
  *
  * Limits and rules:
- *  - B*N*R*(M-2)*8 + 4*B bytes (rounded up to 16) must fit in BRK_STATIC_SCRATCH_BYTES (4 MiB; e.g.
- *    8 prompts x 32 heads x 2 rows x 1000 documents); larger problems are refused with
+ *  - 16384 + B*N*R*(M-2)*8 bytes must fit in BRK_STATIC_SCRATCH_BYTES (4 MiB; e.g. 8 prompts x 32
+ *    heads x 2 rows x 1000 documents) and B*(Nk+1) <= 4096; larger problems are refused with
  *    BRK_E_WORKSPACE and a message that names both sizes.  Each GPU that loads the library holds
  *    the array until exit.
  *  - The first call on a device looks up the array's device address; make that first call

@@ -145,8 +145,17 @@ def _hf_weights(rk):
 
 def test_7b_architecture_prompt_vs_fp32_oracle():
     """One prompt of 64 + 20 x 160 + 48 tokens through layers 0..20 of the Mistral-7B architecture (hidden 4096,
-    32/8 heads, MLP 14336, random bf16 weights N(0, 0.02)): the bf16 CUDA runner against the fp32 oracle on the
-    host, both reading the same weights (scripts/eval_attn.py:135-151 is the loop being reproduced)."""
+    32/8 heads, MLP 14336, random weights N(0, 0.02) rounded to bf16) against the fp32 oracle on the host reading
+    the same weights (scripts/eval_attn.py:135-151 is the loop being reproduced).
+
+    Random weights give nearly uniform document scores (logits 1.0 +- 0.05 with gaps down to 1e-4 between
+    neighbours), so two statements are checked:
+      * the runner in fp32 (the kernels' fp32 paths, same weights): logits within 1e-4 relative of the oracle;
+      * the runner in bf16 (tensor-core attention, bf16 GEMMs): logits within 1e-2 relative;
+      * for both, the top-10 order: identical whenever the oracle's smallest gap among its top 11 exceeds four
+        times the run's largest logit error; otherwise (printed as NEAR TIE) a differing position must hold two
+        documents whose oracle scores are closer than twice that error -- the oracle's order up to ties the
+        arithmetic cannot resolve."""
     cfg = RankerConfig.mistral_7b(20)
     rk = MistralPrefillRanker(cfg, "cuda", torch.bfloat16).init_random(seed=3)
     bl = [64] + [160] * 20 + [48]
@@ -163,9 +172,22 @@ def test_7b_architecture_prompt_vs_fp32_oracle():
         pos[0, off:off + n] = base + torch.arange(n)
         off += n
     rows = torch.tensor([[T - 2, T - 1]], dtype=torch.int32)
-    logits, _ = rk.score(ids.cuda(), pos.cuda(), start.cuda(), ln.cuda(), mbl, rows.cuda(), max_query_len=bl[-1])
+    args = (ids.cuda(), pos.cuda(), start.cuda(), ln.cuda(), mbl, rows.cuda())
+    logits16, _ = rk.score(*args, max_query_len=bl[-1])
     ops.check_status()
-    logits = logits.float().cpu()
+    logits16 = logits16.float().cpu()
+    # the same weights, upcast, through the fp32 paths of the same runner
+    rk32 = MistralPrefillRanker(cfg, "cuda", torch.float32)
+    rk32.embed = rk.embed.float()
+    rk32.layers = [{k: v.float() for k, v in L.items()} for L in rk.layers]
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        logits32, _ = rk32.score(*args, max_query_len=bl[-1])
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    ops.check_status()
+    logits32 = logits32.float().cpu()
     # the same prompt on the reference's left-padded (M, H) grid for the oracle
     idx = H_.packed_to_padded(bl, Hp)
     mask = H_.ragged_mask(1, M, Hp, [bl])
@@ -174,17 +196,34 @@ def test_7b_architecture_prompt_vs_fp32_oracle():
     labels = torch.full((1, M * Hp), -100, dtype=torch.long)
     labels[:, -1] = 7
     ocfg = {"n_heads": 32, "n_kv_heads": 8, "head_dim": 128, "rope_theta": cfg.rope_theta, "rms_eps": cfg.rms_norm_eps}
+    del rk32
     with torch.no_grad():
-        ref_logits, _, _ = orc.mistral_prefill_scores(_hf_weights(rk), ocfg, ids_d, pos_d, mask, labels, 20)
-    ref_logits = ref_logits.float()
-    rel = ((logits - ref_logits).abs() / ref_logits.abs()).max().item()
-    srt = ref_logits.sort(-1, descending=True).values
+        ref, _, _ = orc.mistral_prefill_scores(_hf_weights(rk), ocfg, ids_d, pos_d, mask, labels, 20)
+    ref = ref.float()
+    srt = ref.sort(-1, descending=True).values
     gap = (srt[:, :10] - srt[:, 1:11]).min().item()
-    err = (logits - ref_logits).abs().max().item()
-    print(f"7B-architecture prompt: logits max rel err {rel:.3e}, max abs err {err:.3e}, "
-          f"oracle's smallest gap among its top 11 {gap:.3e}" + ("  (near tie: gap < 2 x err)" if gap < 2 * err else ""))
-    assert rel < 1e-2, rel
-    assert torch.equal(orc.topk_docs(logits), orc.topk_docs(ref_logits))
+    rel32 = ((logits32 - ref).abs() / ref.abs()).max().item()
+    rel16 = ((logits16 - ref).abs() / ref.abs()).max().item()
+    err16 = (logits16 - ref).abs().max().item()
+    err32 = (logits32 - ref).abs().max().item()
+    top_ref, top32, top16 = orc.topk_docs(ref)[0], orc.topk_docs(logits32)[0], orc.topk_docs(logits16)[0]
+
+    def same_order(top, err, what):
+        """Identical top-10 where the oracle separates neighbours by more than the arithmetic's error; where it
+        does not (a tie for that precision), a position may hold the other document of the tie."""
+        swaps = [(int(a), int(b)) for a, b in zip(top, top_ref) if a != b]
+        print(f"  {what}: logit error {err:.3e}; oracle's smallest gap in its top 11 {gap:.3e}; "
+              f"{'well separated' if gap > 4 * err else 'NEAR TIE for this precision'}; differing positions {swaps}")
+        if gap > 4 * err:
+            assert not swaps, swaps
+        for a, b in swaps:
+            assert abs(ref[0, a].item() - ref[0, b].item()) < 2 * err, (what, a, b, ref[0, a].item(), ref[0, b].item(), err)
+
+    print(f"7B-architecture prompt: fp32 logits max rel err {rel32:.3e}; bf16 logits max rel err {rel16:.3e}")
+    assert rel32 < 1e-4, rel32
+    same_order(top32, err32, "fp32 runner")
+    assert rel16 < 1e-2, rel16
+    same_order(top16, err16, "bf16 runner")
 
 
 def test_bounded_wait_gives_up_and_is_reported():

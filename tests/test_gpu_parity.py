@@ -37,7 +37,7 @@ def _run_attn(q, k, v, mask, scaling, algo, lse=False):
 
 def test_library_loads_on_device():
     L = _lib.lib()
-    assert L.brk_version() == 100
+    assert L.brk_version() >= 101
     assert L.brk_device_check() == 0, L.brk_last_error()
 
 
