@@ -83,7 +83,7 @@ constexpr int BN = 64;   // keys per slot (one TMA box)
 constexpr int BT = 128;  // keys per MMA tile (two slots)
 constexpr int HD = 128;  // head dim
 constexpr int kSlots = 5;        // 64-key K/V slots in shared memory
-constexpr int kMaxGroup = 4;     // consecutive blocks of one (prompt, KV head) per work item, at most
+constexpr int kMaxGroup = 4;  // consecutive blocks of one (prompt, KV head) per work item, at most
 constexpr int kThreads = 352;
 constexpr uint32_t kQBytes = 2 * BM * 128;       // one Q tile: two 64-wide halves of D
 constexpr uint32_t kSlotHalf = BN * 128;         // K (or V) of one slot, one 64-wide half of D
@@ -101,10 +101,13 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kChainCols = 256;  // per chain: S [0,128) (P over its first 64 columns), then O [128,256)
 constexpr uint32_t kColO = 128;
 constexpr float kLazy = 8.f;
+// Exponentials per 8 evaluated as a Cody-Waite polynomial on the FMA pipe instead of the special-function unit:
+// 0, 2 or 4.  Measured on the 100-document workload (4 prompts per launch): 0 -> 0.58 ms, 4 -> 0.64 ms; the
+// softmax warps are bound by instruction issue, not by the special-function unit, so the default is 0.
 #ifndef BRK_POLY_OF_8
-#define BRK_POLY_OF_8 4
+#define BRK_POLY_OF_8 0
 #endif
-constexpr int kPolyOf8 = BRK_POLY_OF_8;  // exponentials per 8 evaluated as a polynomial on the FMA pipe: 0, 2 or 4
+constexpr int kPolyOf8 = BRK_POLY_OF_8;
 constexpr uint32_t kWaitBudget = 1u << 18;
 constexpr int kTileFixedCost = 136;  // cost of a row tile beyond its keys (output drain), in keys
 
@@ -121,7 +124,7 @@ enum {
   kJobFree = kJobFull + 2 * kJobRing,     // +chain*kJobRing+i  MMA warp + 4 softmax warps -> TMA warp (5 arrivals)
   kNumBars = kJobFree + 2 * kJobRing
 };
-static_assert(kNumBars * 8 + 16 <= 512, "barrier area");  // + the TMEM base address and the tensor-pipe token
+static_assert(kNumBars * 8 + 8 <= 512, "barrier area");  // + the TMEM base address
 
 // Division by a run-time constant with a host-computed reciprocal (round-up method, exact for every
 // 32-bit numerator): q = umulhi(n, mul); n / d = (((n - q) >> 1) + q) >> shift.
@@ -366,7 +369,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* smem = smem_raw + (sbase - raw);
   const uint32_t sBar = sbase + kOffBar;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + kNumBars * 8);
-  int* const pipe_token = reinterpret_cast<int*>(smem + kOffBar + kNumBars * 8 + 8);
   auto bar = [&](int i) { return sBar + (uint32_t)i * 8u; };
 
   bool failed = false;
@@ -378,7 +380,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (i >= kJobFree) cnt = 5u;                                                        // MMA warp + four softmax warps
       ptx::mbar_init(bar(i), cnt);
     }
-    *pipe_token = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmQ);
     ptx::prefetch_tmap(&tmK);
@@ -646,21 +647,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait(kKVFull + s, (full_par >> s) & 1u, 22 + x);
       full_par ^= 1u << s;
     };
-    // The tensor pipe executes MMAs in the order they were issued, whoever issued them.  A chain's P V and
-    // next Q K^T are issued under a token, so the two chains' groups do not interleave: the chain that asks
-    // first gets its S tile back after ONE group instead of two, which keeps the chains half a round apart
-    // (one in its softmax while the other's MMAs run) instead of in lock step.
-    auto pipe_acquire = [&]() {
-      if (leader) {
-        uint32_t spins = 0;
-        while (atomicCAS(pipe_token, 0, 1) != 0 && ++spins < kWaitBudget) {}  // a spin that runs out just goes ahead
-      }
-      __syncwarp();
-    };
-    auto pipe_release = [&]() {
-      __syncwarp();
-      if (leader) atomicExch(pipe_token, 0);
-    };
     // S = Q K^T against `keys` keys starting at pool slot `slot`
     auto issue_qk = [&](int slot, int keys, bool last) {
       const uint32_t idesc = idesc_qk0 | ((uint32_t)((keys + 15) >> 4) << 18);  // N/8 at bit 17, N a multiple of 16
@@ -747,11 +733,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (T > 0) {
           if (!pre_qk) {
             ensure(min(n, 2));
-            pipe_acquire();
-            ptx::tc_fence_after_sync();
+              ptx::tc_fence_after_sync();
             issue_qk(0, keys_of(0), T == 1);
-            pipe_release();
-            if (T == 1) request_next_q(job_no);
+              if (T == 1) request_next_q(job_no);
           }
           pre_qk = false;
           for (int t = 0; t < T; ++t) {
@@ -773,8 +757,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                            __all_sync(0xffffffffu, ptx::mbar_test(bar(kQFull + x), q_uses & 1u));
               }
             }
-            pipe_acquire();
-            ptx::tc_fence_after_sync();
+              ptx::tc_fence_after_sync();
             issue_pv(2 * t, keys_of(t), t == 0);
             // the chain's next S tile: queued behind the P V that reads P out of the same columns
             if (t + 1 < T) issue_qk(2 * t + 2, keys_of(t + 1), t + 2 == T);
@@ -784,8 +767,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               pre_qk = true;
               ++q_uses;  // its Q tile has landed (tested above): that phase is consumed here
             }
-            pipe_release();
-            if (t + 2 == T) request_next_q(job_no);  // the job's last Q K^T is in the pipe
+              if (t + 2 == T) request_next_q(job_no);  // the job's last Q K^T is in the pipe
           }
           ++jobs_done;
         }
@@ -807,10 +789,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         };
         if (T > 0) {
           need_kv(0);
-          pipe_acquire();
           ptx::tc_fence_after_sync();
           issue_qk(2 * (it.tile0 & 1), keys_of(0), T == 1);
-          pipe_release();
           if (T == 1) request_next_q(job_no);
         }
         for (int t = 0; t < Ti; ++t) {
@@ -820,13 +800,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             wait(kPFull + x, p_seen, 24 + x);
             ++p_seen;
             if (t == 0 && jobs_done > 0) wait(kOFree + x, jobs_done - 1, 26 + x);
-            pipe_acquire();
-            ptx::tc_fence_after_sync();
+              ptx::tc_fence_after_sync();
             issue_pv(slot, keys_of(t), t == 0);
             if (leader) ptx::mma_commit(bar(kKVFree + slot));
             if (t + 1 < T) issue_qk(2 * ((it.tile0 + t + 1) & 1), keys_of(t + 1), t + 2 == T);
-            pipe_release();
-            if (t + 2 == T) request_next_q(job_no);  // the job's last Q K^T is in the pipe
+              if (t + 2 == T) request_next_q(job_no);  // the job's last Q K^T is in the pipe
           } else {
             need_kv(t);  // not visible to this chain: consume the phase, then hand the tile back
             if (leader) ptx::mma_commit(bar(kKVFree + slot));
@@ -965,9 +943,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               }
               ptx::tmem_wait_st();
             }
-            // p with packed fp32x2 arithmetic.  Every second pair of exponentials is evaluated on the
-            // FMA pipe: the special-function unit (16 results per clock per SM) would otherwise bound
-            // the whole kernel.
+            // p with packed fp32x2 arithmetic; see kPolyOf8 for where the exponentials are evaluated
             const ptx::f32x2 sc2 = ptx::pack2(a.scale_log2, a.scale_log2), nr2 = ptx::pack2(neg_ref, neg_ref);
             ptx::f32x2 ps2[2] = {0ull, 0ull};
             uint32_t pk[32];
@@ -1252,9 +1228,10 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
     configured[dev] = true;
   }
   // Blocks are handed out in groups of consecutive blocks of one (prompt, KV head), so that the prefix's K/V
-  // stays in shared memory from one block to the next; the groups shrink when there are too few blocks to
-  // keep every SM busy for several rounds.
-  int group = (int)((nbg * (p.M > 1 ? p.M - 1 : 0)) / (6 * (int64_t)sms[dev]));
+  // stays in shared memory from one block to the next.  Balance matters more than that reuse (measured: single
+  // blocks 0.560 ms, groups of three 0.572 ms on 4 prompts of 100 documents), so groups only form when every SM
+  // still gets two dozen of them.
+  int group = (int)((nbg * (p.M > 1 ? p.M - 1 : 0)) / (24 * (int64_t)sms[dev]));
   group = group < 1 ? 1 : (group > kMaxGroup ? kMaxGroup : group);
   const int n_groups = p.M > 1 ? (p.M - 1 + group - 1) / group : 0;
   const int64_t sec1 = nbg * ns * pairs_q;

@@ -97,6 +97,23 @@ def test_block_shapes_vs_oracle(bl):
     _check_against_oracle(c, B=2, canary=True)
 
 
+def test_many_blocks_grouped_with_resident_prefix():
+    """Enough blocks (8 prompts x 8 KV heads x 111 blocks) for the kernel to hand them out in groups of
+    consecutive blocks whose prefix K/V stays in shared memory from one block to the next: the tensor-core
+    kernel against the CUDA-core kernel (itself checked against the oracle above)."""
+    bl = [100] + [150, 64, 33, 160, 97] * 22 + [48]
+    B = 8
+    start, ln, S, mbl = H_.packed_spans([bl] * B)
+    T = sum(bl)
+    g = torch.Generator(device="cuda").manual_seed(8)
+    mk = lambda h: (torch.randn(B, S, h, D, generator=g, device="cuda") * 0.5).bfloat16().transpose(1, 2)
+    q, k, v = mk(N), mk(NK), mk(NK)
+    o_tc = ops.attention(q, k, v, start.cuda(), ln.cuda(), D ** -0.5, mbl, algo=TC, max_query_len=48)
+    o_si = ops.attention(q, k, v, start.cuda(), ln.cuda(), D ** -0.5, mbl, algo=SIMT)
+    ops.check_status()
+    assert (o_tc.float() - o_si.float())[:, :T].abs().max().item() < 2e-2
+
+
 def test_large_finite_values_in_padding_slots_do_not_leak():
     """Keys outside a row's visible set get probability exactly zero, so finite garbage in the padding slots of
     K/V (here 1e30 behind every block of a padded grid) cannot reach a valid output row."""
@@ -151,7 +168,9 @@ def test_7b_architecture_prompt_vs_fp32_oracle():
     Random weights give nearly uniform document scores (logits 1.0 +- 0.05 with gaps down to 1e-4 between
     neighbours), so two statements are checked:
       * the runner in fp32 (the kernels' fp32 paths, same weights): logits within 1e-4 relative of the oracle;
-      * the runner in bf16 (tensor-core attention, bf16 GEMMs): logits within 1e-2 relative;
+      * the runner in bf16 (tensor-core attention, bf16 GEMMs): its scoring layer within 1e-2 relative of the oracle
+        scoring the SAME hidden state (the per-document tolerance on identical inputs), and end to end within 3e-2 of
+        the fp32 oracle (20 layers of bf16 rounding, which the reference's own bf16 run carries as well);
       * for both, the top-10 order: identical whenever the oracle's smallest gap among its top 11 exceeds four
         times the run's largest logit error; otherwise (printed as NEAR TIE) a differing position must hold two
         documents whose oracle scores are closer than twice that error -- the oracle's order up to ties the
@@ -173,7 +192,8 @@ def test_7b_architecture_prompt_vs_fp32_oracle():
         off += n
     rows = torch.tensor([[T - 2, T - 1]], dtype=torch.int32)
     args = (ids.cuda(), pos.cuda(), start.cuda(), ln.cuda(), mbl, rows.cuda())
-    logits16, _ = rk.score(*args, max_query_len=bl[-1])
+    h20 = rk.hidden_before_score_layer(*args[:5], bl[-1])                  # residual stream entering layer 20 (bf16)
+    logits16, _ = rk.score_from_hidden(h20, args[1], args[2], args[3], args[5])
     ops.check_status()
     logits16 = logits16.float().cpu()
     # the same weights, upcast, through the fp32 paths of the same runner
@@ -219,11 +239,30 @@ def test_7b_architecture_prompt_vs_fp32_oracle():
         for a, b in swaps:
             assert abs(ref[0, a].item() - ref[0, b].item()) < 2 * err, (what, a, b, ref[0, a].item(), ref[0, b].item(), err)
 
-    print(f"7B-architecture prompt: fp32 logits max rel err {rel32:.3e}; bf16 logits max rel err {rel16:.3e}")
+    # the scoring layer alone on identical input: the oracle's layer-20 scoring of the hidden state the bf16 run produced
+    w = _hf_weights(rk)
+    hd = torch.zeros(1, M * Hp, cfg.hidden_size).index_copy_(1, idx, h20.float().cpu()[None, :T])
+    p20 = "model.layers.20."
+    xq = orc.rms_norm(hd, w[p20 + "input_layernorm.weight"], cfg.rms_norm_eps)
+    cos, sin = orc.rope_tables(pos_d, 128, cfg.rope_theta)
+    q20 = orc.apply_rope((xq @ w[p20 + "self_attn.q_proj.weight"].T).view(1, M * Hp, 32, 128).transpose(1, 2), cos, sin)
+    k20 = orc.apply_rope((xq @ w[p20 + "self_attn.k_proj.weight"].T).view(1, M * Hp, 8, 128).transpose(1, 2), cos, sin)
+    sig = torch.tensor([[M * Hp - 2, M * Hp - 1]])
+    ref20 = (orc.doc_mass(q20, k20, mask, 128 ** -0.5, sig).mean(dim=(1, 2)) / 0.05).float()
+    rel20 = ((logits16 - ref20).abs() / ref20.abs()).max().item()
+    err20 = (logits16 - ref20).abs().max().item()
+    print(f"7B-architecture prompt: fp32 run vs oracle: logits max rel err {rel32:.3e}; bf16 run vs fp32 oracle end to end "
+          f"{rel16:.3e}; bf16 scoring layer vs the oracle on the same hidden state {rel20:.3e}")
     assert rel32 < 1e-4, rel32
     same_order(top32, err32, "fp32 runner")
-    assert rel16 < 1e-2, rel16
-    same_order(top16, err16, "bf16 runner")
+    assert rel20 < 1e-2, rel20          # the per-document score tolerance, on identical inputs
+    top20 = orc.topk_docs(ref20)[0]
+    for a_, b_ in [(int(a_), int(b_)) for a_, b_ in zip(top16, top20) if a_ != b_]:
+        assert abs(ref20[0, a_].item() - ref20[0, b_].item()) < 2 * err20, (a_, b_, err20)
+    # end to end the bf16 run carries the rounding of 20 decoder layers (about 1 % of the residual stream per layer,
+    # as bench.py's parity line shows for one layer); 3e-2 bounds that accumulation, it is not an op tolerance
+    assert rel16 < 3e-2, rel16
+    same_order(top16, err16, "bf16 runner, end to end")
 
 
 def test_bounded_wait_gives_up_and_is_reported():
