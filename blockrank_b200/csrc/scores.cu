@@ -6,9 +6,11 @@
 //                        the G query heads of the group) and keeps an online
 //                        (max, sum-exp) per signal row; the CTA writes one
 //                        (max, sum) pair per (head, row, document).  fp32 inputs.
-//   doc_partial_mma_kernel  the same for bf16: the (G*R signal rows) x (keys)
+//   doc_partial_mma_kernel  the same for bf16, a CTA walking through several documents
+//                        of one (prompt, KV head): the (G*R signal rows) x (keys)
 //                        products go through warp-level mma (m16n8k16), key
-//                        rows straight from global memory into the B fragments.
+//                        rows straight from global memory into the B fragments,
+//                        requested one group ahead across document boundaries.
 //                        The product is 8-16 rows tall and bound by the K read;
 //                        a tcgen05 tile (M >= 64, operands staged in shared
 //                        memory, result through tensor memory) would add
@@ -20,6 +22,7 @@
 //                        then the mean over heads and rows / temperature.
 //   raw_scores_kernel    compatibility output: raw masked logits of the last R
 //                        slots against every slot.
+#include <algorithm>
 #include <atomic>
 
 #include "brk_common.cuh"
@@ -29,6 +32,8 @@ namespace {
 
 constexpr int kThreads = 160;  // five warps: a 160-token document is one pass
 constexpr int kRowBatch = 8;  // signal rows accumulated per pass over a key
+constexpr int kKeyStages = 4;   // asynchronous key-row copies a lane keeps in flight in the bf16 kernel
+constexpr int kDocsPerCta = 64;  // documents one CTA of the bf16 kernel walks through, at most
 
 struct ScoreArgs {
   View q, k;
@@ -45,6 +50,16 @@ struct ScoreArgs {
   float scale;
 };
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2) {
   const float mn = fmaxf(m, m2);
   const float ref = (mn == -INFINITY) ? 0.f : mn;
@@ -54,7 +69,7 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2)
 
 // Called by every thread of a partial-kernel CTA after its (max, sum) pairs are written.  Two levels of
 // "last one finishes the job", each a counter that atomicInc wraps back to 0 (so the scratch is ready for the
-// next call): the last of the nd document CTAs of a (prompt, KV head) merges the per-document pairs of that
+// next call): the last of the CTAs of a (prompt, KV head) to finish merges the per-document pairs of that
 // group's G*R (head, signal row) rows into the softmax over all document tokens and writes their per-document
 // probability masses; the last of the Nk groups of a prompt then writes the prompt's logits -- the mean over
 // heads and rows of the masses, divided by the temperature, summed in a fixed order.
@@ -64,7 +79,7 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
   __syncthreads();  // every partial of this CTA has been issued
   if (threadIdx.x == 0) {
     __threadfence();  // ... and is visible device-wide before the counter moves
-    is_last = atomicInc(a.done_bg + b * a.Nk + g, (unsigned)nd - 1) == (unsigned)nd - 1;
+    is_last = atomicInc(a.done_bg + b * a.Nk + g, gridDim.x - 1) == gridDim.x - 1;
   }
   __syncthreads();
   if (!is_last) return;
@@ -72,6 +87,10 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int G = a.N / a.Nk, GR = G * a.R;
   constexpr int kHeld = 8;  // pairs per lane kept in registers: one round trip per row up to 256 documents
+  __shared__ float gsum_w[kThreads / 32][32 * kHeld];
+  float gacc[kHeld];  // this warp's rows summed per document: the group's contribution to the logits
+#pragma unroll
+  for (int i = 0; i < kHeld; ++i) gacc[i] = 0.f;
   for (int row = warp; row < GR; row += nwarps) {
     const size_t w = ((size_t)b * a.N + (size_t)g * G) * a.R + row;  // (head g*G + row / R, signal row row % R)
     const float2* p = a.partial + w * nd;
@@ -105,6 +124,7 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
     for (int i = 0; i < kHeld; ++i) {
       const int d = lane + 32 * i;
       if (d < nd) a.mass[w * nd + d] = held[i].y * inv;
+      gacc[i] += held[i].y * inv;
     }
     for (int d = lane + 32 * kHeld; d < nd; d += 32) {
       const float2 x = __ldcg(&p[d]);
@@ -112,7 +132,21 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
     }
   }
   if (a.logits == nullptr) return;
-  __syncthreads();  // this group's masses have been issued
+  // The group's sum over its (head, row) pairs of the first 32*kHeld documents' masses goes where the group's
+  // first row of pairs was (all of them have been read by now): the prompt's last group then adds Nk numbers
+  // per document instead of N*R.
+  if (warp < kThreads / 32) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) gsum_w[warp][lane + 32 * i] = gacc[i];
+  }
+  __syncthreads();  // every row's pairs have been read, every warp's sums are in shared memory
+  float* const gsum = reinterpret_cast<float*>(a.partial + ((size_t)b * a.N + (size_t)g * G) * a.R * nd);
+  for (int d = threadIdx.x; d < min(nd, 32 * kHeld); d += blockDim.x) {
+    float acc = 0.f;
+    for (int wv = 0; wv < min(nwarps, kThreads / 32); ++wv) acc += gsum_w[wv][d];
+    gsum[d] = acc;
+  }
+  __syncthreads();  // this group's masses and sums have been issued
   if (threadIdx.x == 0) {
     __threadfence();
     is_last = atomicInc(a.done_b + b, (unsigned)a.Nk - 1) == (unsigned)a.Nk - 1;
@@ -122,9 +156,14 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
   __threadfence();
   const int NR = a.N * a.R;
   for (int d = threadIdx.x; d < nd; d += blockDim.x) {
-    const float* p = a.mass + (size_t)b * NR * nd + d;
     float acc = 0.f;
-    for (int i = 0; i < NR; ++i) acc += __ldcg(&p[(size_t)i * nd]);
+    if (d < 32 * kHeld) {
+      for (int gg = 0; gg < a.Nk; ++gg)
+        acc += __ldcg(reinterpret_cast<const float*>(a.partial + ((size_t)b * a.N + (size_t)gg * G) * a.R * nd) + d);
+    } else {
+      const float* p = a.mass + (size_t)b * NR * nd + d;
+      for (int i = 0; i < NR; ++i) acc += __ldcg(&p[(size_t)i * nd]);
+    }
     a.logits[(size_t)b * nd + d] = acc * a.inv_count_temp;
   }
 }
@@ -260,21 +299,31 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uin
 // q+8) are read from Q with the same 16-byte pattern, so both operands come straight from global
 // memory with fully used sectors and no shared-memory staging.
 template <int D>
-__global__ void __launch_bounds__(kThreads) doc_partial_mma_kernel(ScoreArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) doc_partial_mma_kernel(ScoreArgs a) {
   constexpr int kSteps = D / 32;
-  __shared__ float2 red[kThreads / 32][16];
+  constexpr int kStride = (kThreads / 32) * 8;
+  __shared__ float2 red[2][kThreads / 32][16];
+  __shared__ int s_start[kDocsPerCta], s_len[kDocsPerCta];
+  __shared__ uint4 ring[kKeyStages][kSteps][kThreads];  // every lane copies into and reads back its own 16-byte cells
   const int G = a.N / a.Nk;
   const int GR = G * a.R;
   const int nd = a.M - 2;
-  const int d = blockIdx.x;
   const int b = blockIdx.y / a.Nk, g = blockIdx.y % a.Nk;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qr = lane >> 2, j = lane & 3;
-  const int start = a.blk_start[(size_t)b * a.M + 1 + d];
-  const int len = a.blk_len[(size_t)b * a.M + 1 + d];
   const float sl2 = a.scale * 1.4426950408889634f;
   const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)g * a.k.sh;
 
+  // This CTA's documents: blockIdx.x, blockIdx.x + gridDim.x, ... (the launch keeps them within kDocsPerCta).
+  const int n_mine = (nd - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  for (int i = tid; i < n_mine; i += kThreads) {
+    const int d = blockIdx.x + i * gridDim.x;
+    s_start[i] = a.blk_start[(size_t)b * a.M + 1 + d];
+    s_len[i] = a.blk_len[(size_t)b * a.M + 1 + d];
+  }
+  __syncthreads();
+
+  unsigned red_par = 0;
   for (int r0 = 0; r0 < GR; r0 += 16) {
     uint4 qa[kSteps], qb[kSteps];  // signal rows r0+qr and r0+qr+8
 #pragma unroll
@@ -291,57 +340,83 @@ __global__ void __launch_bounds__(kThreads) doc_partial_mma_kernel(ScoreArgs a) 
         if (h == 0) qa[st] = v; else qb[st] = v;
       }
     }
-    float m_lo = -INFINITY, l_lo = 0.f, m_hi = -INFINITY, l_hi = 0.f;
-    // The key rows of the next 8-key group are requested before the products of the current one, so a warp
-    // keeps two groups (8 x 16 bytes per lane) in flight: the kernel is bound by the latency of these loads.
-    constexpr int kStride = (kThreads / 32) * 8;
-    auto load_keys = [&](int base, uint4 (&kf)[kSteps]) {
-      const int key = min(base + qr, len - 1);  // rows past the end re-read the last key; their columns are dropped below
-      const __nv_bfloat16* kp = kbase + (int64_t)(start + key) * a.k.ss + 8 * j;
-#pragma unroll
-      for (int st = 0; st < kSteps; ++st) kf[st] = *reinterpret_cast<const uint4*>(kp + 32 * st);
-    };
-    uint4 kf[kSteps], kn[kSteps];
-    if (warp * 8 < len) load_keys(warp * 8, kf);
-    for (int base = warp * 8; base < len; base += kStride) {
-      if (base + kStride < len) load_keys(base + kStride, kn);
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int st = 0; st < kSteps; ++st) {
-        mma_bf16_16x8x16(c, qa[st].x, qb[st].x, qa[st].y, qb[st].y, kf[st].x, kf[st].y);
-        mma_bf16_16x8x16(c, qa[st].z, qb[st].z, qa[st].w, qb[st].w, kf[st].z, kf[st].w);
+    // A warp visits the 8-key groups (document i, keys base..base+7), base = 8*warp, 8*warp + 40, ..., of
+    // every document of the CTA in order.  The key rows travel through a ring of kKeyStages asynchronous
+    // copies per lane (16 bytes each, global -> shared, read back by the lane that requested them), issued
+    // kKeyStages - 1 groups ahead of the products and across document boundaries: the kernel is bound by the
+    // latency of these loads, and this is what keeps enough of them in flight.
+    int ci = 0, cbase = warp * 8;  // the group requested next
+    auto seek = [&]() {
+      while (ci < n_mine && cbase >= s_len[ci]) {
+        ++ci;
+        cbase = warp * 8;
       }
-      // c[0], c[1]: row qr, keys base + 2j, 2j + 1; c[2], c[3]: row qr + 8, same keys
+    };
+    auto request = [&](int stage) {
+      seek();
+      if (ci < n_mine) {
+        const int key = min(cbase + qr, s_len[ci] - 1);  // rows past the end re-read the last key; their columns are dropped below
+        const __nv_bfloat16* kp = kbase + (int64_t)(s_start[ci] + key) * a.k.ss + 8 * j;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        if (base + 2 * j + e < len) {
-          merge_ml(m_lo, l_lo, c[e] * sl2, 1.f);
-          merge_ml(m_hi, l_hi, c[2 + e] * sl2, 1.f);
+        for (int st = 0; st < kSteps; ++st) cp_async16(&ring[stage][st][tid], kp + 32 * st);
+        cbase += kStride;
+      }
+      cp_async_commit();  // (an empty group when the documents are exhausted: the count below stays uniform)
+    };
+#pragma unroll
+    for (int s = 0; s < kKeyStages - 1; ++s) request(s);
+    int stage_r = 0, stage_w = kKeyStages - 1;
+    for (int i = 0; i < n_mine; ++i) {
+      const int len = s_len[i];
+      float m_lo = -INFINITY, l_lo = 0.f, m_hi = -INFINITY, l_hi = 0.f;
+      for (int base = warp * 8; base < len; base += kStride) {
+        request(stage_w);
+        stage_w = stage_w + 1 == kKeyStages ? 0 : stage_w + 1;
+        cp_async_wait<kKeyStages - 1>();  // the oldest group -- this one -- has landed
+        uint4 kf[kSteps];
+#pragma unroll
+        for (int st = 0; st < kSteps; ++st) kf[st] = ring[stage_r][st][tid];
+        stage_r = stage_r + 1 == kKeyStages ? 0 : stage_r + 1;
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int st = 0; st < kSteps; ++st) {
+          mma_bf16_16x8x16(c, qa[st].x, qb[st].x, qa[st].y, qb[st].y, kf[st].x, kf[st].y);
+          mma_bf16_16x8x16(c, qa[st].z, qb[st].z, qa[st].w, qb[st].w, kf[st].z, kf[st].w);
+        }
+        // c[0], c[1]: row qr, keys base + 2j, 2j + 1; c[2], c[3]: row qr + 8, same keys
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          if (base + 2 * j + e < len) {
+            merge_ml(m_lo, l_lo, c[e] * sl2, 1.f);
+            merge_ml(m_hi, l_hi, c[2 + e] * sl2, 1.f);
+          }
         }
       }
+      // the four lanes of a row, then the warps, in a fixed order
 #pragma unroll
-      for (int st = 0; st < kSteps; ++st) kf[st] = kn[st];
-    }
-    // the four lanes of a row, then the warps, in a fixed order
-#pragma unroll
-    for (int off = 1; off <= 2; off <<= 1) {
-      const float m2 = __shfl_xor_sync(0xffffffffu, m_lo, off), l2 = __shfl_xor_sync(0xffffffffu, l_lo, off);
-      merge_ml(m_lo, l_lo, m2, l2);
-      const float m3 = __shfl_xor_sync(0xffffffffu, m_hi, off), l3 = __shfl_xor_sync(0xffffffffu, l_hi, off);
-      merge_ml(m_hi, l_hi, m3, l3);
-    }
-    __syncthreads();  // red[] of the previous row batch has been read
-    if (j == 0) {
-      red[warp][qr] = make_float2(m_lo, l_lo);
-      red[warp][qr + 8] = make_float2(m_hi, l_hi);
-    }
-    __syncthreads();
-    if (tid < 16 && r0 + tid < GR) {
-      float mm = -INFINITY, ll = 0.f;
-      for (int w = 0; w < kThreads / 32; ++w) merge_ml(mm, ll, red[w][tid].x, red[w][tid].y);
-      const int row = r0 + tid;
-      const int n = g * G + row / a.R, r = row % a.R;
-      a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
+      for (int off = 1; off <= 2; off <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m_lo, off), l2 = __shfl_xor_sync(0xffffffffu, l_lo, off);
+        merge_ml(m_lo, l_lo, m2, l2);
+        const float m3 = __shfl_xor_sync(0xffffffffu, m_hi, off), l3 = __shfl_xor_sync(0xffffffffu, l_hi, off);
+        merge_ml(m_hi, l_hi, m3, l3);
+      }
+      // red[] alternates between documents: a buffer is rewritten two documents later, behind the barrier of
+      // the document in between, which its readers reach only after reading it
+      float2 (&rd)[kThreads / 32][16] = red[red_par];
+      red_par ^= 1u;
+      if (j == 0) {
+        rd[warp][qr] = make_float2(m_lo, l_lo);
+        rd[warp][qr + 8] = make_float2(m_hi, l_hi);
+      }
+      __syncthreads();
+      if (tid < 16 && r0 + tid < GR) {
+        float mm = -INFINITY, ll = 0.f;
+        for (int w = 0; w < kThreads / 32; ++w) merge_ml(mm, ll, rd[w][tid].x, rd[w][tid].y);
+        const int row = r0 + tid;
+        const int n = g * G + row / a.R, r = row % a.R;
+        const int d = blockIdx.x + i * gridDim.x;
+        a.partial[(((size_t)b * a.N + n) * a.R + r) * nd + d] = make_float2(mm, ll);
+      }
     }
   }
   finalize_if_last(a, b, g);
@@ -472,14 +547,29 @@ static int doc_scores_run(const brk_score_params& p, void* ws, size_t ws_bytes, 
   const size_t pitch = (size_t)p.D * (p.dtype == BRK_BF16 ? 2 : 4) + 16;
   const size_t sm = (size_t)G * p.R * p.D * 4 + (kThreads / 32) * kRowBatch * sizeof(float2) + (kThreads / 32) * 32 * pitch;
   auto launch = [&](auto kern) -> int {
-    if (sm > 48 * 1024) BRK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    // (the kernels also hold a few KB of static shared memory, which counts against the same 48 KB default)
+    if (sm + 8192 > 48 * 1024) BRK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
     kern<<<grid, kThreads, sm, st>>>(a);
     BRK_CUDA(cudaGetLastError());
     return BRK_OK;
   };
   if (p.dtype == BRK_BF16) {
-    if (p.D == 128) doc_partial_mma_kernel<128><<<grid, kThreads, 0, st>>>(a);
-    else doc_partial_mma_kernel<64><<<grid, kThreads, 0, st>>>(a);
+    // A CTA walks through several documents so that its key loads overlap across document boundaries; the
+    // grid is sized to be resident at once (four CTAs per SM) when there are enough documents for that.
+    const int slots = 4 * std::max(1, sm_count());
+    int per_bg = std::max(1, slots / (p.B * p.Nk));
+    per_bg = std::min(nd, std::max(per_bg, (nd + kDocsPerCta - 1) / kDocsPerCta));
+    dim3 grid_docs(per_bg, p.B * p.Nk);
+    // (four CTAs with their key rings need 170 KB of shared memory per SM: ask for the large carve-out)
+    if (p.D == 128) {
+      BRK_CUDA(cudaFuncSetAttribute(doc_partial_mma_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    (int)cudaSharedmemCarveoutMaxShared));
+      doc_partial_mma_kernel<128><<<grid_docs, kThreads, 0, st>>>(a);
+    } else {
+      BRK_CUDA(cudaFuncSetAttribute(doc_partial_mma_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    (int)cudaSharedmemCarveoutMaxShared));
+      doc_partial_mma_kernel<64><<<grid_docs, kThreads, 0, st>>>(a);
+    }
     BRK_CUDA(cudaGetLastError());
     return BRK_OK;
   }
@@ -541,7 +631,8 @@ int raw_scores_launch(const brk_score_params& p, void* out, cudaStream_t st) {
   dim3 grid((p.S + kThreads - 1) / kThreads, p.B * p.Nk);
   const size_t sm = (size_t)G * p.R * p.D * 4 + p.R * sizeof(int);
   auto launch = [&](auto kern, auto* o, float neg) -> int {
-    if (sm > 48 * 1024) BRK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+    // (the kernels also hold a few KB of static shared memory, which counts against the same 48 KB default)
+    if (sm + 8192 > 48 * 1024) BRK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
     kern<<<grid, kThreads, sm, st>>>(a, o, neg);
     BRK_CUDA(cudaGetLastError());
     return BRK_OK;
