@@ -67,6 +67,14 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2)
   m = mn;
 }
 
+// two more logits (already in log2 units; -inf = masked) into a running (max, sum)
+__device__ __forceinline__ void merge_pair(float& m, float& l, float x0, float x1) {
+  const float mn = fmaxf(m, fmaxf(x0, x1));
+  const float ref = (mn == -INFINITY) ? 0.f : mn;
+  l = l * exp2f(m - ref) + (exp2f(x0 - ref) + exp2f(x1 - ref));
+  m = mn;
+}
+
 // Called by every thread of a partial-kernel CTA after its (max, sum) pairs are written.  Two levels of
 // "last one finishes the job", each a counter that atomicInc wraps back to 0 (so the scratch is ready for the
 // next call): the last of the CTAs of a (prompt, KV head) to finish merges the per-document pairs of that
@@ -325,6 +333,32 @@ __global__ void __launch_bounds__(kThreads, 4) doc_partial_mma_kernel(ScoreArgs 
 
   unsigned red_par = 0;
   for (int r0 = 0; r0 < GR; r0 += 16) {
+    // A warp visits the 8-key groups (document i, keys base..base+7), base = 8*warp, 8*warp + 40, ..., of
+    // every document of the CTA in order.  The key rows travel through a ring of kKeyStages asynchronous
+    // copies per lane (16 bytes each, global -> shared, read back by the lane that requested them), issued
+    // kKeyStages - 1 groups ahead of the products and across document boundaries: the kernel is bound by the
+    // latency of these loads, and this is what keeps enough of them in flight.
+    int ci = -1, cbase = 0, clen = 0;  // the group requested next: keys cbase.. of the CTA's document ci (clen keys)
+    const __nv_bfloat16* cptr = kbase;  // first key row of that document, this lane's 16-byte column
+    auto request = [&](int stage) {
+      while (ci < n_mine && cbase >= clen) {  // next document that still has a group for this warp
+        ++ci;
+        cbase = warp * 8;
+        clen = ci < n_mine ? s_len[ci] : 0;
+        if (ci < n_mine) cptr = kbase + (int64_t)s_start[ci] * a.k.ss + 8 * j;
+      }
+      if (ci < n_mine) {
+        const int key = min(cbase + qr, clen - 1);  // rows past the end re-read the last key; their columns are dropped below
+        const __nv_bfloat16* kp = cptr + (int64_t)key * a.k.ss;
+#pragma unroll
+        for (int st = 0; st < kSteps; ++st) cp_async16(&ring[stage][st][tid], kp + 32 * st);
+        cbase += kStride;
+      }
+      cp_async_commit();  // (an empty group when the documents are exhausted: the count below stays uniform)
+    };
+#pragma unroll
+    for (int s = 0; s < kKeyStages - 1; ++s) request(s);
+    // (the signal rows of Q are read behind the first key requests: both latencies overlap)
     uint4 qa[kSteps], qb[kSteps];  // signal rows r0+qr and r0+qr+8
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -340,31 +374,6 @@ __global__ void __launch_bounds__(kThreads, 4) doc_partial_mma_kernel(ScoreArgs 
         if (h == 0) qa[st] = v; else qb[st] = v;
       }
     }
-    // A warp visits the 8-key groups (document i, keys base..base+7), base = 8*warp, 8*warp + 40, ..., of
-    // every document of the CTA in order.  The key rows travel through a ring of kKeyStages asynchronous
-    // copies per lane (16 bytes each, global -> shared, read back by the lane that requested them), issued
-    // kKeyStages - 1 groups ahead of the products and across document boundaries: the kernel is bound by the
-    // latency of these loads, and this is what keeps enough of them in flight.
-    int ci = 0, cbase = warp * 8;  // the group requested next
-    auto seek = [&]() {
-      while (ci < n_mine && cbase >= s_len[ci]) {
-        ++ci;
-        cbase = warp * 8;
-      }
-    };
-    auto request = [&](int stage) {
-      seek();
-      if (ci < n_mine) {
-        const int key = min(cbase + qr, s_len[ci] - 1);  // rows past the end re-read the last key; their columns are dropped below
-        const __nv_bfloat16* kp = kbase + (int64_t)(s_start[ci] + key) * a.k.ss + 8 * j;
-#pragma unroll
-        for (int st = 0; st < kSteps; ++st) cp_async16(&ring[stage][st][tid], kp + 32 * st);
-        cbase += kStride;
-      }
-      cp_async_commit();  // (an empty group when the documents are exhausted: the count below stays uniform)
-    };
-#pragma unroll
-    for (int s = 0; s < kKeyStages - 1; ++s) request(s);
     int stage_r = 0, stage_w = kKeyStages - 1;
     for (int i = 0; i < n_mine; ++i) {
       const int len = s_len[i];
@@ -384,13 +393,9 @@ __global__ void __launch_bounds__(kThreads, 4) doc_partial_mma_kernel(ScoreArgs 
           mma_bf16_16x8x16(c, qa[st].z, qb[st].z, qa[st].w, qb[st].w, kf[st].z, kf[st].w);
         }
         // c[0], c[1]: row qr, keys base + 2j, 2j + 1; c[2], c[3]: row qr + 8, same keys
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          if (base + 2 * j + e < len) {
-            merge_ml(m_lo, l_lo, c[e] * sl2, 1.f);
-            merge_ml(m_hi, l_hi, c[2 + e] * sl2, 1.f);
-          }
-        }
+        const bool ok0 = base + 2 * j < len, ok1 = base + 2 * j + 1 < len;
+        merge_pair(m_lo, l_lo, ok0 ? c[0] * sl2 : -INFINITY, ok1 ? c[1] * sl2 : -INFINITY);
+        merge_pair(m_hi, l_hi, ok0 ? c[2] * sl2 : -INFINITY, ok1 ? c[3] * sl2 : -INFINITY);
       }
       // the four lanes of a row, then the warps, in a fixed order
 #pragma unroll
