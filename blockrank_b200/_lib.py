@@ -17,7 +17,8 @@ ERRORS = {-1: "BRK_E_ARG", -2: "BRK_E_UNSUPPORTED", -3: "BRK_E_WORKSPACE", -4: "
           -5: "BRK_E_DEVICE", -6: "BRK_E_TIMEOUT"}
 
 EXPORTS = ("brk_version", "brk_last_error", "brk_device_check", "brk_spans_from_mask",
-           "brk_attn_fwd_workspace_bytes", "brk_attn_fwd", "brk_status_poll", "brk_selftest_bounded_wait",
+           "brk_attn_fwd_workspace_bytes", "brk_attn_fwd", "brk_attn_bwd_workspace_bytes", "brk_attn_bwd",
+           "brk_status_poll", "brk_selftest_bounded_wait",
            "brk_doc_scores_workspace_bytes",
            "brk_doc_scores", "brk_doc_scores_static", "brk_raw_scores", "brk_rmsnorm", "brk_rope", "brk_silu_mul")
 
@@ -32,6 +33,13 @@ class AttnParams(C.Structure):
                 ("scale", C.c_float), ("q", View), ("k", View), ("v", View), ("o", View),
                 ("lse", C.c_void_p), ("blk_start", C.c_void_p), ("blk_len", C.c_void_p), ("status", C.c_void_p),
                 ("max_query_len", C.c_int32)]
+
+
+class AttnBwdParams(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("B", C.c_int32), ("N", C.c_int32), ("Nk", C.c_int32), ("D", C.c_int32),
+                ("S", C.c_int32), ("M", C.c_int32), ("max_block_len", C.c_int32), ("scale", C.c_float),
+                ("q", View), ("k", View), ("v", View), ("o", View), ("d_o", View), ("lse", C.c_void_p),
+                ("blk_start", C.c_void_p), ("blk_len", C.c_void_p), ("dq", View), ("dk", View), ("dv", View)]
 
 
 class ScoreParams(C.Structure):
@@ -68,6 +76,10 @@ def lib() -> C.CDLL:
     L.brk_attn_fwd_workspace_bytes.argtypes = [C.POINTER(AttnParams)]
     L.brk_attn_fwd.restype = C.c_int
     L.brk_attn_fwd.argtypes = [C.POINTER(AttnParams), C.c_void_p, C.c_size_t, C.c_void_p]
+    L.brk_attn_bwd_workspace_bytes.restype = C.c_size_t
+    L.brk_attn_bwd_workspace_bytes.argtypes = [C.POINTER(AttnBwdParams)]
+    L.brk_attn_bwd.restype = C.c_int
+    L.brk_attn_bwd.argtypes = [C.POINTER(AttnBwdParams), C.c_void_p, C.c_size_t, C.c_void_p]
     L.brk_status_poll.restype = C.c_int
     L.brk_status_poll.argtypes = [C.c_void_p, C.c_void_p]
     L.brk_selftest_bounded_wait.restype = C.c_int

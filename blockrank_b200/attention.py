@@ -15,8 +15,12 @@ Differences that matter to callers:
     ``attention_mask`` is used as it is (padding-free layout);
   * K/V heads are shared inside the kernel (no ``repeat_kv`` copy) and the
     output is written directly as ``(B, S, N, D)``;
-  * forward only: autograd through it raises NotImplementedError, like the
-    reference's Triton path (triton:759-761).
+  * training: under autograd the attention output and the raw last-rows
+    logits are differentiable (``brk_attn_bwd`` and two skinny products),
+    which is what the auxiliary-loss trainer needs
+    (src/blockrank/trainer.py:51-107, src/blockrank/losses.py:37-93); the
+    reference's Triton path has no backward at all (triton:759-761).  The
+    fused ``blockrank_doc_scores`` output is inference-only.
 """
 from __future__ import annotations
 
@@ -64,6 +68,50 @@ def cuda_blockrank_attention_mask(*args, attention_mask: Optional[torch.Tensor] 
     return BlockSpans.make(start, length, attention_mask.shape[-1], grid_h=attention_mask.shape[-1])
 
 
+class _AttentionFn(torch.autograd.Function):
+    """BlockRank attention with its backward: forward keeps (q, k, v, out, lse), backward is ``brk_attn_bwd``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, start, length, scale, max_block_len, max_query_len, algo):
+        out, lse = ops.attention(q, k, v, start, length, scale, max_block_len, return_lse=True, algo=algo,
+                                 max_query_len=max_query_len)
+        ctx.save_for_backward(q, k, v, out, lse, start, length)
+        ctx.scale, ctx.max_block_len = float(scale), int(max_block_len)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse, start, length = ctx.saved_tensors
+        dq, dk, dv = ops.attention_bwd(q, k, v, out, d_out.to(out.dtype), lse, start, length, ctx.scale,
+                                       ctx.max_block_len)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+class _RawScoresFn(torch.autograd.Function):
+    """Raw logits of the last R slots, (B,N,R,S) = scale * q[:, :, S-R:] k^T + a constant mask addend
+    (std:219-233, 256-262), with the gradient autograd gives the reference: the addend is constant, so
+    d raw flows to q and k at every position."""
+
+    @staticmethod
+    def forward(ctx, q, k, start, length, scale, num_last, grid_h):
+        raw = ops.raw_scores(q, k, start, length, scale, num_last, grid_h=grid_h)
+        ctx.save_for_backward(q, k)
+        ctx.scale = float(scale)
+        return raw
+
+    @staticmethod
+    def backward(ctx, d_raw):
+        q, k = ctx.saved_tensors
+        B, N, S, D = q.shape
+        Nk, R = k.shape[1], d_raw.shape[2]
+        g = (d_raw.float() * ctx.scale).view(B, Nk, N // Nk, R, S)
+        q_last = q[:, :, S - R:].float().reshape(B, Nk, N // Nk, R, D)
+        dq = torch.zeros(B, N, S, D, dtype=q.dtype, device=q.device)
+        dq[:, :, S - R:] = torch.einsum("bkgrs,bksd->bkgrd", g, k.float()).reshape(B, N, R, D).to(q.dtype)
+        dk = torch.einsum("bkgrs,bkgrd->bksd", g, q_last).to(k.dtype)
+        return dq, dk, None, None, None, None, None
+
+
 def _wants_scores(module, kwargs) -> bool:
     # same precedence as std:244-254
     layers = kwargs.get("layers_to_return_scores", None)
@@ -91,23 +139,32 @@ def cuda_blockrank_attention_forward(module, query, key, value, attention_mask, 
         if attention_mask is None:
             raise ValueError("BlockRank attention requires block spans (got attention_mask=None)")
         attention_mask = cuda_blockrank_attention_mask(attention_mask=attention_mask, **kwargs)
-    if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
-        raise NotImplementedError("cuda_blockrank attention is forward-only; run under torch.no_grad()")
+    train = torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad)
     if dropout and getattr(module, "training", False):
         warnings.warn("cuda_blockrank attention ignores attention dropout")
     spans = attention_mask
     start, length = spans[0], spans[1]
-    out = ops.attention(query, key, value, start, length, scaling, spans.max_block_len,
-                        algo=kwargs.get("blockrank_algo", _lib.ALGO_AUTO),
-                        max_query_len=getattr(spans, "max_query_len", 0))
+    algo = kwargs.get("blockrank_algo", _lib.ALGO_AUTO)
+    if train:
+        out = _AttentionFn.apply(query, key, value, start, length, scaling, spans.max_block_len,
+                                 getattr(spans, "max_query_len", 0), algo)
+    else:
+        out = ops.attention(query, key, value, start, length, scaling, spans.max_block_len, algo=algo,
+                            max_query_len=getattr(spans, "max_query_len", 0))
     scores = None
     if start.shape[-1] > 1 and _wants_scores(module, kwargs):
         if kwargs.get("blockrank_doc_scores", False):
+            if train:
+                raise NotImplementedError("blockrank_doc_scores=True is inference-only; train on the raw scores "
+                                          "(compute_auxiliary_attention_loss differentiates them)")
             rows = kwargs.get("signal_rows")
             if rows is None:
                 raise ValueError("blockrank_doc_scores=True needs signal_rows (B, R) slot indices")
             scores, _ = ops.doc_scores(query, key, start, length, rows.to(device=query.device, dtype=torch.int32),
                                        scaling, kwargs.get("temperature", 0.05))
+        elif train:
+            scores = _RawScoresFn.apply(query, key, start, length, scaling, kwargs.get("num_last_queries", 16),
+                                        getattr(spans, "grid_h", None))
         else:
             scores = ops.raw_scores(query, key, start, length, scaling, kwargs.get("num_last_queries", 16),
                                     grid_h=getattr(spans, "grid_h", None))

@@ -99,6 +99,38 @@ int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t workspace_byt
   return BRK_E_UNSUPPORTED;
 }
 
+static int check_attn_bwd(const brk_attn_bwd_params* p) {
+  BRK_REQUIRE(p != nullptr, BRK_E_ARG, "params is null");
+  BRK_REQUIRE(p->dtype == BRK_BF16 || p->dtype == BRK_F32, BRK_E_UNSUPPORTED, "dtype %d not supported", p->dtype);
+  BRK_REQUIRE(p->B > 0 && p->N > 0 && p->Nk > 0 && p->S > 0 && p->M > 0, BRK_E_ARG,
+              "bad shape B=%d N=%d Nk=%d S=%d M=%d", p->B, p->N, p->Nk, p->S, p->M);
+  BRK_REQUIRE(p->N % p->Nk == 0, BRK_E_ARG, "N=%d is not a multiple of Nk=%d", p->N, p->Nk);
+  BRK_REQUIRE(64 % (p->N / p->Nk) == 0, BRK_E_UNSUPPORTED, "query heads per KV head (%d) must divide 64", p->N / p->Nk);
+  BRK_REQUIRE(p->D == 64 || p->D == 128, BRK_E_UNSUPPORTED, "head_dim %d not supported (64 or 128)", p->D);
+  BRK_REQUIRE(p->max_block_len > 0 && p->max_block_len <= p->S, BRK_E_ARG, "max_block_len=%d out of range (S=%d)",
+              p->max_block_len, p->S);
+  BRK_REQUIRE(p->blk_start && p->blk_len && p->lse, BRK_E_ARG, "block spans / lse are null");
+  BRK_REQUIRE(p->scale > 0.f, BRK_E_ARG, "softmax scale must be positive");
+  const brk_view* vs[8] = {&p->q, &p->k, &p->v, &p->o, &p->d_o, &p->dq, &p->dk, &p->dv};
+  const char* names[8] = {"q", "k", "v", "o", "d_o", "dq", "dk", "dv"};
+  for (int i = 0; i < 8; ++i) {
+    const int rc = check_view(*vs[i], p->dtype, names[i]);
+    if (rc) return rc;
+  }
+  return BRK_OK;
+}
+
+size_t brk_attn_bwd_workspace_bytes(const brk_attn_bwd_params* p) {
+  if (p == nullptr) return 0;
+  return attn_bwd_workspace(*p);
+}
+
+int brk_attn_bwd(const brk_attn_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_attn_bwd(p);
+  if (rc) return rc;
+  return attn_bwd_launch(*p, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
 int brk_status_poll(int32_t* status, void* stream) {
   BRK_REQUIRE(status != nullptr, BRK_E_ARG, "status is null");
   int32_t v = 0;

@@ -111,6 +111,8 @@ int attn_simt_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaSt
 int selftest_wait_launch(int32_t* status, uint32_t budget, cudaStream_t st);
 int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t attn_tc_workspace(const brk_attn_params& p);
+size_t attn_bwd_workspace(const brk_attn_bwd_params& p);
+int attn_bwd_launch(const brk_attn_bwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
 int sm_count();
 
 }  // namespace brk

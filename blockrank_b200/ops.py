@@ -137,6 +137,46 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, blk_start: torc
     return (out, lse) if (return_lse or lse is not None) else out
 
 
+def attention_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, d_out: torch.Tensor,
+                  lse: torch.Tensor, blk_start: torch.Tensor, blk_len: torch.Tensor, scale: float, max_block_len: int):
+    """Gradients of :func:`attention` (what autograd derives from the reference's eager / SDPA paths,
+    src/blockrank/blockrank_std_attention.py:96-262, 472-650).
+
+    q (B,N,S,D), k/v (B,Nk,S,D) as given to the forward; out / d_out (B,S,N,D); lse (B,N,S) fp32 from the
+    forward.  Returns (dq (B,N,S,D), dk, dv (B,Nk,S,D)) in the input dtype; slots outside every block get zeros.
+    """
+    _need_cuda(q, k, v, out, d_out, lse, blk_start, blk_len)
+    B, N, S, D = q.shape
+    Nk = k.shape[1]
+    if out.shape != (B, S, N, D) or d_out.shape != out.shape:
+        raise ValueError(f"out / d_out must be (B,S,N,D) = {(B, S, N, D)}, got {tuple(out.shape)} / {tuple(d_out.shape)}")
+    if lse.shape != (B, N, S) or lse.dtype != torch.float32:
+        raise ValueError("lse must be the forward's fp32 (B, N, S) tensor")
+    if any(t.dtype != q.dtype for t in (k, v, out, d_out)):
+        raise ValueError("q, k, v, out, d_out must share a dtype")
+    d_out, lse = d_out.contiguous(), lse.contiguous()  # (autograd may hand over expanded or transposed gradients)
+    dq = torch.empty(B, S, N, D, dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
+    dk = torch.empty(B, S, Nk, D, dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
+    dv = torch.empty(B, S, Nk, D, dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
+    p = _lib.AttnBwdParams()
+    p.dtype = _dtype_code(q)
+    p.B, p.N, p.Nk, p.D, p.S, p.M = B, N, Nk, D, S, blk_start.shape[-1]
+    p.max_block_len, p.scale = int(max_block_len), float(scale)
+    p.q, p.k, p.v = _view(q), _view(k), _view(v)
+    p.o, p.d_o = _view(out.permute(0, 2, 1, 3)), _view(d_out.permute(0, 2, 1, 3))
+    p.lse = lse.data_ptr()
+    bs, bl = blk_start.contiguous(), blk_len.contiguous()
+    p.blk_start, p.blk_len = bs.data_ptr(), bl.data_ptr()
+    p.dq, p.dk, p.dv = _view(dq), _view(dk), _view(dv)
+    L = _lib.lib()
+    with torch.cuda.device(q.device):
+        nbytes = L.brk_attn_bwd_workspace_bytes(C.byref(p))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        _lib.check(L.brk_attn_bwd(C.byref(p), ws.data_ptr(), nbytes, _stream(q)), "brk_attn_bwd")
+    _count(3)  # dq (+ delta), dk/dv accumulation, conversion of the accumulators
+    return dq, dk, dv
+
+
 def _score_params(q, k, blk_start, blk_len, scale, R, temperature=0.05) -> _lib.ScoreParams:
     B, N, S, D = q.shape
     p = _lib.ScoreParams()

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define BRK_VERSION 101
+#define BRK_VERSION 102
 
 #if defined(__GNUC__)
 #define BRK_API __attribute__((visibility("default")))
@@ -118,6 +118,30 @@ BRK_API int brk_spans_from_mask(const uint8_t* mask, int32_t B, int32_t M, int32
  * the partial results of the query block's key chunks for long prompts. */
 BRK_API size_t brk_attn_fwd_workspace_bytes(const brk_attn_params* p);
 BRK_API int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Backward of the attention call, for training through the registered attention function.  Replaces what
+ * autograd derives from the reference's differentiable paths (eager_blockrank_attention_forward and
+ * sdpa_blockrank_attention_forward, src/blockrank/blockrank_std_attention.py:96-262, 472-650; the reference's
+ * Triton path has no backward, src/blockrank/blockrank_triton_kernel_attention.py:759-761), as used by the
+ * auxiliary-loss trainer (src/blockrank/trainer.py:51-107).
+ * Inputs are the forward's q, k, v, its output o and its lse ([B, N, S], natural log) and the gradient d_o of o
+ * (same layout as o).  Outputs dq (like q), dk and dv (like k, v; summed over the query heads of each KV group);
+ * slots outside every block get zero gradients.  CUDA-core kernels with fp32 accumulation for both dtypes. */
+typedef struct brk_attn_bwd_params {
+  int32_t dtype;          /* BRK_BF16 or BRK_F32 (q, k, v, o, d_o, dq, dk, dv share it) */
+  int32_t B, N, Nk, D;    /* D = 64 or 128; N / Nk must divide 64 */
+  int32_t S, M, max_block_len;
+  float scale;
+  brk_view q, k, v, o, d_o;
+  const float* lse;       /* [B, N, S] from the forward call */
+  const int32_t* blk_start;
+  const int32_t* blk_len;
+  brk_view dq, dk, dv;    /* written through their strides; dk, dv: (B, Nk, S, D) views */
+} brk_attn_bwd_params;
+
+/* fp32 scratch: the rows' dot(d_o, o) and the dk / dv accumulators; cleared by the call */
+BRK_API size_t brk_attn_bwd_workspace_bytes(const brk_attn_bwd_params* p);
+BRK_API int brk_attn_bwd(const brk_attn_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Device-side status.  The kernels never trap: a bounded wait that gives up, or malformed block spans, set
  * the caller's status word (brk_attn_params.status; first event wins) and the kernel returns normally.
