@@ -228,3 +228,64 @@ def test_rank_items_matches_score_topk():
         assert preds[i] == torch.topk(logits[0], 5).indices.tolist()
     m = metrics.ranking_metrics(preds, [p[0] for p in preds])
     assert m["accuracy"] == 100.0
+
+
+def test_hf_registry_training_step_gradients(golden_dir):
+    """A training step as the auxiliary-loss trainer makes it (src/blockrank/trainer.py:51-107): LM loss plus the
+    InfoNCE loss over the per-document logits of layer l* (src/blockrank/losses.py:37-93), back-propagated through
+    the registered CUDA attention.  Parameter gradients are compared with the same model run through a plain
+    PyTorch attention over the oracle's pair predicate (autograd does the backward there)."""
+    import copy
+    from transformers import AttentionInterface, AttentionMaskInterface
+    from blockrank_b200.attention import cuda_blockrank_attention_mask
+    fx = _load(golden_dir, "tiny_mistral")
+    base = _tiny_hf_model().float()
+    L = int(fx["score_layer"])
+    ids = torch.from_numpy(fx["input_ids"]).cuda()
+    pos = torch.from_numpy(fx["position_ids"]).cuda()
+    mask_cpu = torch.from_numpy(fx["mask"])
+    mask = mask_cpu.cuda()
+    labels = torch.from_numpy(fx["labels"]).cuda()
+    B, M, Hh = mask.shape
+    S = M * Hh
+    ok = orc.allowed_pairs(mask_cpu).cuda()                       # (B, S, S)
+    valid = mask.reshape(B, S)
+    ok_safe = ok | ((~valid)[:, :, None] & torch.eye(S, dtype=torch.bool, device="cuda")[None])
+    answers = torch.tensor([[1, 3]] * B).cuda()
+
+    def torch_attention(module, query, key, value, attention_mask, scaling, dropout=0.0, **kw):
+        g = query.shape[1] // key.shape[1]
+        kx, vx = key.repeat_interleave(g, dim=1), value.repeat_interleave(g, dim=1)
+        s = torch.matmul(query, kx.transpose(-1, -2)) * scaling
+        out = torch.matmul(torch.softmax(s.masked_fill(~ok_safe[:, None], float("-inf")), dim=-1), vx)
+        out = out.transpose(1, 2) * valid[:, :, None, None]
+        raw = None
+        if kw.get("layers_to_return_scores") and module.layer_idx in kw["layers_to_return_scores"]:
+            R = min(16, Hh)
+            raw = s[:, :, S - R:] + torch.where(ok[:, None, S - R:], 0.0, 0.7 * torch.finfo(s.dtype).min)
+        return out, raw
+
+    AttentionInterface.register("torch_ref_blockrank", torch_attention)
+    AttentionMaskInterface.register("torch_ref_blockrank", cuda_blockrank_attention_mask)
+    name = register_cuda_blockrank_attention()
+
+    def step(impl):
+        model = copy.deepcopy(base)
+        model.set_attn_implementation(impl)
+        model = model.cuda().train()
+        out = model(input_ids=ids, position_ids=pos, attention_mask=mask, labels=labels, output_attentions=True,
+                    layers_to_return_scores=[L])
+        raw = out.attentions[0].float()
+        logits = orc.doc_scores_from_raw(raw, labels, mask)          # (B, docs), differentiable
+        pos_mask = torch.zeros_like(logits, dtype=torch.bool).scatter_(1, answers, True)
+        aux = -(torch.logsumexp(logits.masked_fill(~pos_mask, float("-inf")), 1) - torch.logsumexp(logits, 1)).mean()
+        loss = out.loss + 0.1 * aux
+        loss.backward()
+        return loss.item(), aux.item(), {n: p.grad.detach().double().cpu() for n, p in model.named_parameters() if p.grad is not None}
+
+    loss_c, aux_c, g_c = step(name)
+    loss_t, aux_t, g_t = step("torch_ref_blockrank")
+    assert abs(loss_c - loss_t) < 1e-4 * abs(loss_t) and abs(aux_c - aux_t) < 1e-4 * max(1.0, abs(aux_t))
+    assert g_c.keys() == g_t.keys() and len(g_c) > 20
+    worst = max(((g_c[n] - g_t[n]).norm() / g_t[n].norm().clamp_min(1e-12)).item() for n in g_t)
+    assert worst < 1e-3, worst
