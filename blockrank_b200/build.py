@@ -16,7 +16,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libblockrank_b200.so")
-SOURCES = ["brk_api.cu", "attn_simt.cu", "attn_tc.cu", "attn_bwd.cu", "scores.cu", "elementwise.cu"]
+SOURCES = ["brk_api.cu", "attn_simt.cu", "attn_tc.cu", "attn_bwd.cu", "attn_bwd_mma.cu", "scores.cu", "elementwise.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

@@ -1,5 +1,6 @@
 // BlockRank attention backward on CUDA cores (fp32 accumulate), for training through the registered
-// attention function.  The reference gets these gradients from autograd over its eager / SDPA paths
+// attention function: the fp32 path, and the entry point that sends bf16 to the tensor-core kernels of
+// attn_bwd_mma.cu.  The reference gets these gradients from autograd over its eager / SDPA paths
 // (src/blockrank/blockrank_std_attention.py:96-262, 472-650); the mathematics is that of the softmax
 // attention backward restricted to each row's visible keys:
 //
@@ -311,7 +312,11 @@ int launch_all(const BwdArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-size_t attn_bwd_workspace(const brk_attn_bwd_params& p) { return delta_bytes(p) + 2 * acc_bytes(p); }
+// (bf16 only) fp32 dq of the last block's rows, shared by the CTAs that split its keys
+size_t dq_last_bytes(const brk_attn_bwd_params& p) {
+  return p.dtype == BRK_BF16 ? (size_t)p.B * p.N * p.max_block_len * p.D * sizeof(float) : 0;
+}
+size_t attn_bwd_workspace(const brk_attn_bwd_params& p) { return delta_bytes(p) + 2 * acc_bytes(p) + dq_last_bytes(p); }
 
 int attn_bwd_launch(const brk_attn_bwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
   BRK_REQUIRE(ws != nullptr && ws_bytes >= attn_bwd_workspace(p) && ((uintptr_t)ws & 15) == 0, BRK_E_WORKSPACE,
@@ -326,12 +331,20 @@ int attn_bwd_launch(const brk_attn_bwd_params& p, void* ws, size_t ws_bytes, cud
   a.dv32 = a.dk32 + (size_t)p.B * p.Nk * p.S * p.D;
   a.blk_start = p.blk_start; a.blk_len = p.blk_len;
   a.B = p.B; a.N = p.N; a.Nk = p.Nk; a.S = p.S; a.M = p.M; a.G = p.N / p.Nk; a.max_block_len = p.max_block_len;
-  a.nsplit = p.M > 2 ? std::min(p.M, 16) : 1;
+  a.nsplit = p.M > 2 ? std::min(p.M, 64) : 1;  // block 0 is seen by every row block: its key tiles need many CTAs
   a.scale = p.scale;
   a.scale_log2 = p.scale * 1.4426950408889634f;
-  BRK_CUDA(cudaMemsetAsync(w + delta_bytes(p), 0, 2 * acc_bytes(p), st));
-  if (p.dtype == BRK_BF16)
-    return p.D == 128 ? launch_all<__nv_bfloat16, 128>(a, st) : launch_all<__nv_bfloat16, 64>(a, st);
+  BRK_CUDA(cudaMemsetAsync(w + delta_bytes(p), 0, 2 * acc_bytes(p) + dq_last_bytes(p), st));
+  if (p.dtype == BRK_BF16) {
+    // bf16: the tensor-core kernels compute dq and the accumulators; the conversion kernel is shared
+    int rc = attn_bwd_mma_launch(p, a.delta, a.dk32, a.dv32, a.dv32 + (size_t)p.B * p.Nk * p.S * p.D, st);
+    if (rc) return rc;
+    const int64_t n4 = (int64_t)a.B * a.Nk * a.S * (p.D / 4);
+    const int blocks = (int)std::min<int64_t>((n4 + 255) / 256, 148 * 16);
+    attn_bwd_store_kernel<__nv_bfloat16><<<std::max(blocks, 1), 256, 0, st>>>(a, p.D);
+    BRK_CUDA(cudaGetLastError());
+    return BRK_OK;
+  }
   return p.D == 128 ? launch_all<float, 128>(a, st) : launch_all<float, 64>(a, st);
 }
 

@@ -105,7 +105,8 @@ static int check_attn_bwd(const brk_attn_bwd_params* p) {
   BRK_REQUIRE(p->B > 0 && p->N > 0 && p->Nk > 0 && p->S > 0 && p->M > 0, BRK_E_ARG,
               "bad shape B=%d N=%d Nk=%d S=%d M=%d", p->B, p->N, p->Nk, p->S, p->M);
   BRK_REQUIRE(p->N % p->Nk == 0, BRK_E_ARG, "N=%d is not a multiple of Nk=%d", p->N, p->Nk);
-  BRK_REQUIRE(64 % (p->N / p->Nk) == 0, BRK_E_UNSUPPORTED, "query heads per KV head (%d) must divide 64", p->N / p->Nk);
+  BRK_REQUIRE(p->dtype == BRK_BF16 || 64 % (p->N / p->Nk) == 0, BRK_E_UNSUPPORTED,
+              "fp32 backward: query heads per KV head (%d) must divide 64", p->N / p->Nk);
   BRK_REQUIRE(p->D == 64 || p->D == 128, BRK_E_UNSUPPORTED, "head_dim %d not supported (64 or 128)", p->D);
   BRK_REQUIRE(p->max_block_len > 0 && p->max_block_len <= p->S, BRK_E_ARG, "max_block_len=%d out of range (S=%d)",
               p->max_block_len, p->S);

@@ -113,6 +113,7 @@ int attn_tc_launch(const brk_attn_params& p, void* ws, size_t ws_bytes, cudaStre
 size_t attn_tc_workspace(const brk_attn_params& p);
 size_t attn_bwd_workspace(const brk_attn_bwd_params& p);
 int attn_bwd_launch(const brk_attn_bwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
+int attn_bwd_mma_launch(const brk_attn_bwd_params& p, float* delta, float* dk32, float* dv32, float* dq32, cudaStream_t st);
 int sm_count();
 
 }  // namespace brk

@@ -126,10 +126,11 @@ BRK_API int brk_attn_fwd(const brk_attn_params* p, void* workspace, size_t works
  * auxiliary-loss trainer (src/blockrank/trainer.py:51-107).
  * Inputs are the forward's q, k, v, its output o and its lse ([B, N, S], natural log) and the gradient d_o of o
  * (same layout as o).  Outputs dq (like q), dk and dv (like k, v; summed over the query heads of each KV group);
- * slots outside every block get zero gradients.  CUDA-core kernels with fp32 accumulation for both dtypes. */
+ * slots outside every block get zero gradients.  bf16: warp-level tensor-core MMA (fp32 accumulation);
+ * fp32: CUDA cores (there N / Nk must divide 64). */
 typedef struct brk_attn_bwd_params {
   int32_t dtype;          /* BRK_BF16 or BRK_F32 (q, k, v, o, d_o, dq, dk, dv share it) */
-  int32_t B, N, Nk, D;    /* D = 64 or 128; N / Nk must divide 64 */
+  int32_t B, N, Nk, D;    /* D = 64 or 128 */
   int32_t S, M, max_block_len;
   float scale;
   brk_view q, k, v, o, d_o;
@@ -139,7 +140,7 @@ typedef struct brk_attn_bwd_params {
   brk_view dq, dk, dv;    /* written through their strides; dk, dv: (B, Nk, S, D) views */
 } brk_attn_bwd_params;
 
-/* fp32 scratch: the rows' dot(d_o, o) and the dk / dv accumulators; cleared by the call */
+/* fp32 scratch: the rows' dot(d_o, o), the dk / dv accumulators and (bf16) the last block's dq; cleared by the call */
 BRK_API size_t brk_attn_bwd_workspace_bytes(const brk_attn_bwd_params* p);
 BRK_API int brk_attn_bwd(const brk_attn_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
 

@@ -86,6 +86,8 @@ def main():
     ap.add_argument("--impl", default="all")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--prompts", type=int, default=0, help="override the config's prompt count (profiling runs)")
+    ap.add_argument("--backward", action="store_true",
+                    help="time forward + backward instead (impls: ours, eager_ref, sdpa_ref; the Triton path has none)")
     a = ap.parse_args()
     from baseline import ref_loader
     from blockrank_b200 import _lib, ops
@@ -123,6 +125,9 @@ def main():
         if note:
             line["note"] = note
         print(json.dumps(line), flush=True)
+
+    if a.backward:
+        return backward_bench(a, ops, ref_loader, q, k, v, mask, start, ln, scale, H, S, prompts, bl, flops, valid)
 
     for name in impls:
         try:
@@ -181,6 +186,54 @@ def main():
             tb = traceback.format_exc().strip().splitlines()
             print(json.dumps({"config": a.config, "impl": name, "unavailable": f"{type(e).__name__}: {e}"[:400],
                               "where": tb[-3:] if len(tb) >= 3 else tb}), flush=True)
+            torch.cuda.synchronize()
+
+
+def backward_bench(a, ops, ref_loader, q, k, v, mask, start, ln, scale, H, S, prompts, bl, flops, valid):
+    """Forward + backward of the attention op under autograd: this library (tcgen05 forward, CUDA-core backward)
+    beside autograd over the reference's eager and SDPA functions, same tensors, gradients compared."""
+    from blockrank_b200.attention import _AttentionFn
+    from blockrank_b200 import _lib
+    g = torch.Generator(device=q.device).manual_seed(4)
+    d_out = (torch.randn(prompts, S, N, D, generator=g, device=q.device) * valid[:, :, None, None]).bfloat16()
+    impls = ["ours", "eager_ref", "sdpa_ref"] if a.impl == "all" else a.impl.split(",")
+    base = None
+    for name in impls:
+        try:
+            qg, kg, vg = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+            if name == "ours":
+                run = lambda: _AttentionFn.apply(qg, kg, vg, start, ln, scale, H, 0, _lib.ALGO_AUTO)
+            else:
+                if not ref_loader.available():
+                    raise RuntimeError(ref_loader.why_unavailable())
+                std = ref_loader.load("std")
+                mod = ref_loader.AttnModule(N // NK)
+                add = std.eager_blockrank_attention_mask(prompts, None, S, attention_mask=mask, dtype=torch.bfloat16)
+                fwd = std.sdpa_blockrank_attention_forward if name == "sdpa_ref" else std.eager_blockrank_attention_forward
+                run = lambda: fwd(mod, qg, kg, vg, add, scale)[0]
+
+            def step():
+                for t in (qg, kg, vg):
+                    t.grad = None
+                run().backward(d_out)
+
+            with torch.enable_grad():
+                ms = timeit(step, a.iters)
+                step()
+            grads = [t.grad.float() for t in (qg, kg, vg)]
+            line = {"config": a.config, "impl": name, "mode": "forward+backward", "prompts": prompts,
+                    "tokens_per_prompt": sum(bl), "ms_median": ms[0], "ms_min": ms[1],
+                    "tflops_exact_fwd_plus_2.5x": 3.5 * flops / ms[0] / 1e9}
+            if base is None:
+                base = grads
+            else:
+                vm = valid[:, None, :, None]
+                line["grad_rel_diff_vs_first"] = [float(((x - y) * vm).norm() / (y * vm).norm()) for x, y in zip(grads, base)]
+            print(json.dumps(line), flush=True)
+        except Exception as e:
+            tb = traceback.format_exc().strip().splitlines()
+            print(json.dumps({"config": a.config, "impl": name, "mode": "forward+backward",
+                              "unavailable": f"{type(e).__name__}: {e}"[:400], "where": tb[-3:]}), flush=True)
             torch.cuda.synchronize()
 
 
