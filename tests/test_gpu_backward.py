@@ -96,11 +96,20 @@ def test_attention_backward_fp32_vs_oracle_autograd(name, lens, H, N, Nk, D):
         assert dv.cpu().permute(0, 2, 1, 3)[pad].abs().max() == 0
 
 
-def test_attention_backward_bf16_tensor_core_forward():
-    """bf16, head_dim 128, 4 query heads per KV head: the forward (and its lse) comes from the tcgen05 kernel."""
+BF16_CASES = [
+    # name, block lengths per prompt, H, N, Nk, D
+    ("tc_forward_gqa4_d128", [[64, 160, 97, 160, 48], [64, 33, 160, 128, 40]], 160, 8, 2, 128),
+    # many blocks: the last block's keys and block 0's rows are split across CTAs
+    ("many_docs_gqa2_d64", [[64] + [96, 70, 96, 13, 96, 80, 96, 96, 55, 96, 96, 31, 96, 90] + [40]], 96, 4, 2, 64),
+    ("one_block_d128", [[150]], 152, 2, 1, 128),
+]
+
+
+@pytest.mark.parametrize("name,lens,H,N,Nk,D", BF16_CASES, ids=[c[0] for c in BF16_CASES])
+def test_attention_backward_bf16(name, lens, H, N, Nk, D):
+    """bf16: backward on warp-level tensor-core MMA; with head_dim 128 and 4 query heads per KV head the forward
+    (and its lse) comes from the tcgen05 kernel."""
     g = torch.Generator().manual_seed(5)
-    lens = [[64, 160, 97, 160, 48], [64, 33, 160, 128, 40]]
-    H, N, Nk, D = 160, 8, 2, 128
     mask = _mask(lens, H)
     B, M, _ = mask.shape
     S = M * H
@@ -112,7 +121,11 @@ def test_attention_backward_bf16_tensor_core_forward():
     _, dq, dk, dv = _run_cuda(q, k, v, mask, scale, d_out, torch.bfloat16)
     for got, ref, what in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
         rel = (got.cpu().double() - ref).norm() / ref.norm()
-        assert rel < 1e-2, (what, rel.item())     # bf16 outputs, fp32 accumulation
+        assert rel < 1e-2, (what, rel.item())     # bf16 operands and outputs, fp32 accumulation
+    pad = ~mask.reshape(B, S)
+    if pad.any():
+        for t in (dq, dk, dv):
+            assert t.float().cpu().permute(0, 2, 1, 3)[pad].abs().max() == 0
 
 
 def test_registered_function_trains_attention_and_raw_scores():
