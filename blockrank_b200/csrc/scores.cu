@@ -338,6 +338,7 @@ __global__ void __launch_bounds__(kThreads, 4) doc_partial_mma_kernel(ScoreArgs 
     // copies per lane (16 bytes each, global -> shared, read back by the lane that requested them), issued
     // kKeyStages - 1 groups ahead of the products and across document boundaries: the kernel is bound by the
     // latency of these loads, and this is what keeps enough of them in flight.
+    const bool has_hi = r0 + 8 < GR;  // with 8 or fewer (head, signal row) pairs left, rows 8..15 of the product are padding
     int ci = -1, cbase = 0, clen = 0;  // the group requested next: keys cbase.. of the CTA's document ci (clen keys)
     const __nv_bfloat16* cptr = kbase;  // first key row of that document, this lane's 16-byte column
     auto request = [&](int stage) {
@@ -395,15 +396,17 @@ __global__ void __launch_bounds__(kThreads, 4) doc_partial_mma_kernel(ScoreArgs 
         // c[0], c[1]: row qr, keys base + 2j, 2j + 1; c[2], c[3]: row qr + 8, same keys
         const bool ok0 = base + 2 * j < len, ok1 = base + 2 * j + 1 < len;
         merge_pair(m_lo, l_lo, ok0 ? c[0] * sl2 : -INFINITY, ok1 ? c[1] * sl2 : -INFINITY);
-        merge_pair(m_hi, l_hi, ok0 ? c[2] * sl2 : -INFINITY, ok1 ? c[3] * sl2 : -INFINITY);
+        if (has_hi) merge_pair(m_hi, l_hi, ok0 ? c[2] * sl2 : -INFINITY, ok1 ? c[3] * sl2 : -INFINITY);
       }
       // the four lanes of a row, then the warps, in a fixed order
 #pragma unroll
       for (int off = 1; off <= 2; off <<= 1) {
         const float m2 = __shfl_xor_sync(0xffffffffu, m_lo, off), l2 = __shfl_xor_sync(0xffffffffu, l_lo, off);
         merge_ml(m_lo, l_lo, m2, l2);
-        const float m3 = __shfl_xor_sync(0xffffffffu, m_hi, off), l3 = __shfl_xor_sync(0xffffffffu, l_hi, off);
-        merge_ml(m_hi, l_hi, m3, l3);
+        if (has_hi) {
+          const float m3 = __shfl_xor_sync(0xffffffffu, m_hi, off), l3 = __shfl_xor_sync(0xffffffffu, l_hi, off);
+          merge_ml(m_hi, l_hi, m3, l3);
+        }
       }
       // red[] alternates between documents: a buffer is rewritten two documents later, behind the barrier of
       // the document in between, which its readers reach only after reading it
