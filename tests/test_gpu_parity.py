@@ -207,9 +207,18 @@ def test_doc_scores_vs_reference_fixture(golden_dir, name):
     rows = torch.tensor([[S - 2, S - 1]] * B, dtype=torch.int32).cuda()
     mass, logits = ops.doc_scores(H_.to_cuda_view(q), H_.to_cuda_view(k), start, ln, rows, float(fx["scaling"]))
     ref = torch.from_numpy(fx["logits"])
-    assert torch.allclose(logits.cpu(), ref, rtol=3e-2 if bf16 else 1e-4, atol=1e-5)
     exact = orc.doc_mass(q, k, mask, float(fx["scaling"]), rows.cpu().long())
     assert torch.allclose(mass.cpu().double(), exact, rtol=1e-3, atol=1e-6)
+    # Logits: the bar is 1e-2 relative.  The kernel is held to 1e-3 of the fp64 closed form; the reference's own
+    # logits (made from raw scores rounded to the working dtype) are further from it in bf16, which is logged, and
+    # the distance between the two must be explained by the reference's distance plus ours.
+    exact_logits = exact.mean(dim=(1, 2)) / 0.05
+    ours_rel = ((logits.cpu().double() - exact_logits).abs() / exact_logits.abs()).max().item()
+    ref_rel = ((ref.double() - exact_logits).abs() / exact_logits.abs()).max().item()
+    print(f"{name}: logits vs fp64 closed form: kernel {ours_rel:.2e}, reference fixture {ref_rel:.2e}")
+    assert ours_rel < 1e-3
+    assert ref_rel < (1e-2 if bf16 else 1e-4)
+    assert ((logits.cpu().double() - ref.double()).abs() <= (ref_rel + 1e-3) * exact_logits.abs() + 1e-6).all()
     assert torch.allclose(mass.sum(-1).cpu(), torch.ones(B, q.shape[1], 2), atol=1e-5)
 
 
@@ -299,7 +308,12 @@ def test_standalone_op_config_parity():
     gap = (srt[:, :10] - srt[:, 1:11]).min().item()
     err = (logits.cpu().double() - exact_logits).abs().max().item()
     print(f"standalone-op scores: max abs err {err:.3e}, min adjacent gap in top-11 {gap:.3e}")
-    assert torch.equal(top_k, top_r) or gap < 10 * err, (gap, err)
+    # identical top-10 where the oracle separates neighbours by more than twice the run's error; in any case the
+    # document ranked p-th by the kernel must be worth the oracle's p-th value up to that error (ties only)
+    if gap > 2 * err:
+        assert torch.equal(top_k, top_r), (gap, err)
+    got_vals = exact_logits.gather(1, top_k.long())
+    assert bool((got_vals >= srt[:, :10] - 2 * err).all()), (gap, err)
 
 
 def _ragged_prompt(n_docs, seed, lo=32, hi=256):
