@@ -86,6 +86,10 @@ def main():
     ap.add_argument("--impl", default="all")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--prompts", type=int, default=0, help="override the config's prompt count (profiling runs)")
+    ap.add_argument("--model", action="store_true",
+                    help="model level: a Hugging Face Mistral (7B geometry, layers 0..20, random bf16) run the way "
+                         "scripts/eval_attn.py runs it, only the registered attention implementation changes "
+                         "(impls: cuda_blockrank, triton_ref, eager_ref, sdpa_ref, runner)")
     ap.add_argument("--backward", action="store_true",
                     help="time forward + backward instead (impls: ours, eager_ref, sdpa_ref; the Triton path has none)")
     a = ap.parse_args()
@@ -126,6 +130,8 @@ def main():
             line["note"] = note
         print(json.dumps(line), flush=True)
 
+    if a.model:
+        return model_bench(a, ops, ref_loader, mask, H, S, prompts, bl)
     if a.backward:
         return backward_bench(a, ops, ref_loader, q, k, v, mask, start, ln, scale, H, S, prompts, bl, flops, valid)
 
@@ -186,6 +192,76 @@ def main():
             tb = traceback.format_exc().strip().splitlines()
             print(json.dumps({"config": a.config, "impl": name, "unavailable": f"{type(e).__name__}: {e}"[:400],
                               "where": tb[-3:] if len(tb) >= 3 else tb}), flush=True)
+            torch.cuda.synchronize()
+
+
+def model_bench(a, ops, ref_loader, mask, H, S, prompts, bl):
+    """The drop-in at model level: one Hugging Face MistralForCausalLM (7B geometry, layers 0..l* = 20, random bf16
+    weights) on the GPU, called as scripts/eval_attn.py:135-151 calls it (lm_head patched to identity, raw scores of
+    layer l* through ``layers_to_return_scores``, the reference's loss function as the reduction); only
+    ``attn_implementation`` changes between the rows.  ``runner`` is this library's lean early-exit runner loaded
+    with the same weights."""
+    from transformers import MistralConfig, MistralForCausalLM
+    from blockrank_b200 import register_cuda_blockrank_attention
+    from blockrank_b200.runner import MistralPrefillRanker, RankerConfig
+    dev = torch.device("cuda")
+    L = 20
+    cfg = MistralConfig(vocab_size=32768, hidden_size=4096, intermediate_size=14336, num_hidden_layers=L + 1,
+                        num_attention_heads=N, num_key_value_heads=NK, head_dim=D, rope_theta=1e6, rms_norm_eps=1e-5,
+                        sliding_window=None, max_position_embeddings=32768)
+    torch.manual_seed(0)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = MistralForCausalLM(cfg).eval()
+    finally:
+        torch.set_default_dtype(old)
+    ident = lambda self_, hidden_states, *x, **kw: hidden_states
+    model.lm_head.forward = ident.__get__(model.lm_head, type(model.lm_head))
+    losses = ref_loader.load("losses") if ref_loader.available() else None
+    g = torch.Generator().manual_seed(7)
+    valid = mask.reshape(prompts, S)
+    ids = torch.randint(3, 32768, (prompts, S), generator=g).to(dev) * valid
+    pos = ((valid.long().cumsum(1) - 1).clamp_min(0)) * valid       # running index over the valid slots
+    labels = torch.full((prompts, S), -100, dtype=torch.long, device=dev)
+    labels[:, -1] = 7
+    names = {"cuda_blockrank": None, "triton_ref": "triton_blockrank", "eager_ref": "eager_blockrank",
+             "sdpa_ref": "sdpa_blockrank"}
+    impls = ["cuda_blockrank", "triton_ref", "eager_ref", "runner"] if a.impl == "all" else a.impl.split(",")
+    base = None
+    for name in impls:
+        try:
+            if name == "runner":
+                rk = MistralPrefillRanker(RankerConfig.mistral_7b(score_layer=L), dev).load_state_dict(model.state_dict())
+                start, ln = ops.spans_from_mask(mask)
+                rows = torch.tensor([[S - 2, S - 1]] * prompts, dtype=torch.int32, device=dev)
+                run = lambda: rk.score(ids, pos, start, ln, H, rows, max_query_len=bl[-1])[0]
+            else:
+                if losses is None:  # the reduction of the raw scores is the reference's own function
+                    raise RuntimeError(ref_loader.why_unavailable())
+                impl = register_cuda_blockrank_attention() if name == "cuda_blockrank" else ref_loader.register(names[name])
+                model.set_attn_implementation(impl)
+
+                def run():
+                    out = model(input_ids=ids, position_ids=pos, attention_mask=mask, output_attentions=True,
+                                layers_to_return_scores=[L])
+                    return losses.compute_auxiliary_attention_loss(out.attentions[0], labels, mask, None, return_logits=True)
+            logits = run().float()
+            ms = timeit(run, a.iters, warmup=2)
+            line = {"config": a.config, "impl": name, "mode": "model (21 layers, 7B geometry, bf16)", "prompts": prompts,
+                    "tokens_per_prompt": sum(bl), "ms_median": ms[0], "ms_min": ms[1],
+                    "prompts_per_s": prompts / ms[0] * 1e3}
+            if base is None:
+                base = logits
+            else:
+                line["logits_max_rel_diff_vs_first"] = float(((logits - base) / base).abs().max())
+                line["top10_equal_first"] = bool(torch.equal(torch.topk(logits, 10).indices, torch.topk(base, 10).indices))
+            print(json.dumps(line), flush=True)
+        except Exception as e:
+            tb = traceback.format_exc().strip().splitlines()
+            print(json.dumps({"config": a.config, "impl": name, "mode": "model", "unavailable": f"{type(e).__name__}: {e}"[:400],
+                              "where": tb[-3:]}), flush=True)
             torch.cuda.synchronize()
 
 
