@@ -572,7 +572,7 @@ def run_ours(args, cfg):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of attn_tc_kernel per prompt of the c4 geometry (profiles/)
-NCU_TRAFFIC_PER_PROMPT = 388.1e6
+NCU_TRAFFIC_PER_PROMPT = 388.3e6
 
 
 def main():

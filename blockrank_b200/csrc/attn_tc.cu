@@ -26,9 +26,10 @@
 //
 // Roles (352 threads):
 //   warps 0-3 / 4-7  softmax + output of chain 0 / 1 (thread = row = TMEM lane)
-//   warp 8           TMA producer: claims and decodes items, publishes jobs, loads Q and K/V
+//   warp 8           TMA producer: claims and decodes items, publishes jobs, loads K/V
 //   warps 9 / 10     MMA issuer of chain 0 / 1: S = Q K^T (both operands K-major, 128B swizzle)
-//                    and O += P V (P read from tensor memory, V as the MN-major B operand)
+//                    and O += P V (P read from tensor memory, V as the MN-major B operand); it also
+//                    requests its chain's Q tiles by TMA (it knows when the Q buffer is free)
 // Softmax is base-2, online, with a lazy rescale (O is only touched when the running max grows
 // by more than 2^8).  P (bf16, two keys per 32-bit column) overwrites the first half of the S
 // tile it was computed from.
