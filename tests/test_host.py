@@ -32,6 +32,27 @@ def test_library_exports_every_declared_symbol():
     assert L.brk_version() == version
 
 
+def test_argument_checks_return_error_codes_without_a_gpu():
+    """Bad arguments are refused by the host-side checks of the C ABI before anything touches a device."""
+    L = _lib.lib()
+    assert L.brk_attn_fwd(None, None, 0, None) == -1                       # BRK_E_ARG: params is null
+    assert L.brk_attn_bwd(None, None, 0, None) == -1
+    assert b"null" in L.brk_last_error()
+    p = _lib.AttnBwdParams()
+    p.dtype, p.B, p.N, p.Nk, p.D, p.S, p.M, p.max_block_len, p.scale = 0, 1, 6, 4, 128, 64, 2, 32, 0.1
+    assert L.brk_attn_bwd(ctypes.byref(p), None, 0, None) == -1             # N is not a multiple of Nk
+    assert b"multiple" in L.brk_last_error()
+    p.N, p.D = 8, 96
+    assert L.brk_attn_bwd(ctypes.byref(p), None, 0, None) == -2             # BRK_E_UNSUPPORTED: head_dim
+    p.D, p.max_block_len = 128, 65
+    assert L.brk_attn_bwd(ctypes.byref(p), None, 0, None) == -1             # max_block_len > S
+    p.max_block_len = 32
+    assert L.brk_attn_bwd(ctypes.byref(p), None, 0, None) == -1             # spans / lse are null
+    assert L.brk_attn_bwd_workspace_bytes(None) == 0
+    # delta [B,N,S] + two fp32 accumulators [B,Nk,S,D] + (bf16) the last block's dq [B,N,max_block_len,D]
+    assert L.brk_attn_bwd_workspace_bytes(ctypes.byref(p)) == 8 * 64 * 4 + 2 * 4 * 64 * 128 * 4 + 8 * 32 * 128 * 4
+
+
 def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libblockrank_b200.so")
