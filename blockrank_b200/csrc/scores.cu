@@ -99,8 +99,9 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
   float gacc[kHeld];  // this warp's rows summed per document: the group's contribution to the logits
 #pragma unroll
   for (int i = 0; i < kHeld; ++i) gacc[i] = 0.f;
+  const size_t w0 = ((size_t)b * a.N + (size_t)g * G) * a.R;  // the group's first (head, signal row) pair
   for (int row = warp; row < GR; row += nwarps) {
-    const size_t w = ((size_t)b * a.N + (size_t)g * G) * a.R + row;  // (head g*G + row / R, signal row row % R)
+    const size_t w = w0 + row;  // (head g*G + row / R, signal row row % R)
     const float2* p = a.partial + w * nd;
     float2 held[kHeld];
 #pragma unroll
@@ -140,9 +141,10 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
     }
   }
   if (a.logits == nullptr) return;
-  // The group's sum over its (head, row) pairs of the first 32*kHeld documents' masses goes where the group's
-  // first row of pairs was (all of them have been read by now): the prompt's last group then adds Nk numbers
-  // per document instead of N*R.
+  // The group's sum over its (head, row) pairs of every document's mass goes where the group's first row of
+  // pairs was (all of them have been read by now): the prompt's last group then adds Nk numbers per document
+  // instead of N*R.  The first 32*kHeld documents come from the registers of the loop above, the rest (long
+  // lists) from the masses this CTA has just written.
   if (warp < kThreads / 32) {
 #pragma unroll
     for (int i = 0; i < kHeld; ++i) gsum_w[warp][lane + 32 * i] = gacc[i];
@@ -154,6 +156,11 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
     for (int wv = 0; wv < min(nwarps, kThreads / 32); ++wv) acc += gsum_w[wv][d];
     gsum[d] = acc;
   }
+  for (int d = 32 * kHeld + threadIdx.x; d < nd; d += blockDim.x) {
+    float acc = 0.f;
+    for (int row = 0; row < GR; ++row) acc += __ldcg(&a.mass[(w0 + row) * nd + d]);
+    gsum[d] = acc;
+  }
   __syncthreads();  // this group's masses and sums have been issued
   if (threadIdx.x == 0) {
     __threadfence();
@@ -162,16 +169,10 @@ __device__ __forceinline__ void finalize_if_last(const ScoreArgs& a, int b, int 
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  const int NR = a.N * a.R;
   for (int d = threadIdx.x; d < nd; d += blockDim.x) {
     float acc = 0.f;
-    if (d < 32 * kHeld) {
-      for (int gg = 0; gg < a.Nk; ++gg)
-        acc += __ldcg(reinterpret_cast<const float*>(a.partial + ((size_t)b * a.N + (size_t)gg * G) * a.R * nd) + d);
-    } else {
-      const float* p = a.mass + (size_t)b * NR * nd + d;
-      for (int i = 0; i < NR; ++i) acc += __ldcg(&p[(size_t)i * nd]);
-    }
+    for (int gg = 0; gg < a.Nk; ++gg)
+      acc += __ldcg(reinterpret_cast<const float*>(a.partial + ((size_t)b * a.N + (size_t)gg * G) * a.R * nd) + d);
     a.logits[(size_t)b * nd + d] = acc * a.inv_count_temp;
   }
 }

@@ -239,6 +239,25 @@ def test_doc_scores_many_rows_and_empty_doc():
     assert torch.allclose(logits.cpu().double(), exact.mean(dim=(1, 2)) / 0.05, rtol=1e-3)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_doc_scores_long_list(dt):
+    """More documents than one warp keeps in registers (> 256): masses and logits of a 300-document list."""
+    B, N, Nk, D, H = 2, 8, 2, 64, 8
+    M = 302
+    lens = H_.random_lens(B, M, H, 77)
+    lens[1][40] = 0
+    mask = H_.ragged_mask(B, M, H, lens)
+    q, k, _ = H_.qkv(B, N, Nk, M * H, D, 78, dt)
+    start, ln = _spans_cuda(mask)
+    S = M * H
+    rows = torch.tensor([[S - 2, S - 1]] * B, dtype=torch.int32)
+    mass, logits = ops.doc_scores(H_.to_cuda_view(q), H_.to_cuda_view(k), start, ln, rows.cuda(), D ** -0.5, 0.05)
+    exact = orc.doc_mass(q, k, mask, D ** -0.5, rows.long())
+    assert torch.allclose(mass.cpu().double(), exact, rtol=1e-3, atol=1e-8)
+    assert torch.allclose(logits.cpu().double(), exact.mean(dim=(1, 2)) / 0.05, rtol=1e-3, atol=1e-8)
+    assert torch.allclose(mass.sum(-1).cpu(), torch.ones(B, N, 2), atol=1e-5)
+
+
 def test_error_codes():
     q, k, v = H_.qkv(1, 4, 2, 32, 96, 1, torch.bfloat16)  # head_dim 96 unsupported
     mask = H_.ragged_mask(1, 2, 16, [[16, 16]])
