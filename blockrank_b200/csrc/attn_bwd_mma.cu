@@ -25,6 +25,9 @@ namespace {
 constexpr int kT = 64;         // tokens (rows or keys) per staged tile
 constexpr int kWarps = 4;
 constexpr int kThreadsM = kWarps * 32;
+// Row-tile buffers of the dk/dv kernel: 1 = the next tile is requested after the current one has been multiplied
+// (70 KB of shared memory, three CTAs per SM cover the copy), 2 = requested before (104 KB, two CTAs per SM).
+constexpr int kRowBufs = 1;
 
 struct BwdMmaArgs {
   View q, k, v, o, d_o, dq;
@@ -166,7 +169,7 @@ __device__ __forceinline__ void mm_nn_acc(float (&acc)[D / 8][4], const uint32_t
 // whose rows see every key of the prompt: y = split instead, the row tile's key tiles are dealt to `ksplit` CTAs
 // and the results are added into the fp32 array dq32 (converted by attn_bwd_store_dq_last_kernel).
 template <int D, bool kLast>
-__global__ void __launch_bounds__(kThreadsM) attn_bwd_dq_mma_kernel(BwdMmaArgs a) {
+__global__ void __launch_bounds__(kThreadsM, 3) attn_bwd_dq_mma_kernel(BwdMmaArgs a) {
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   Tile<D>* const tiles = reinterpret_cast<Tile<D>*>(dyn_smem);  // [0], [1]: Q / dO first, then K / V; [2], [3]: the other K / V buffer
   Tile<D>& t0s = tiles[0];
@@ -362,12 +365,12 @@ __global__ void __launch_bounds__(256) attn_bwd_store_dq_last_kernel(BwdMmaArgs 
 
 // grid: x = 64-key tile of the block, y = key block, z = ((prompt * Nk + KV head) * nsplit + split)
 template <int D>
-__global__ void __launch_bounds__(kThreadsM) attn_bwd_dkv_mma_kernel(BwdMmaArgs a) {
+__global__ void __launch_bounds__(kThreadsM, 3) attn_bwd_dkv_mma_kernel(BwdMmaArgs a) {
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   Tile<D>& ks_t = *reinterpret_cast<Tile<D>*>(dyn_smem);
   Tile<D>& vs_t = *reinterpret_cast<Tile<D>*>(dyn_smem + sizeof(Tile<D>));
   Tile<D>* const row_tiles = reinterpret_cast<Tile<D>*>(dyn_smem + 2 * sizeof(Tile<D>));  // [2 buf]: Q, [2 buf + 1]: dO
-  float* const row_stats = reinterpret_cast<float*>(dyn_smem + 6 * sizeof(Tile<D>));         // [buf][lse: kT | delta: kT]
+  float* const row_stats = reinterpret_cast<float*>(dyn_smem + (2 + 2 * kRowBufs) * sizeof(Tile<D>));  // [buf][lse: kT | delta: kT]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
   const int split = blockIdx.z % a.nsplit, bg = blockIdx.z / a.nsplit;
   const int b = bg / a.Nk, g = bg % a.Nk;
@@ -433,10 +436,15 @@ __global__ void __launch_bounds__(kThreadsM) attn_bwd_dkv_mma_kernel(BwdMmaArgs 
   RowIt nxt = cur;
   int buf = 0;
   while (has) {
-    const bool has_n = advance(nxt);
-    if (has_n) issue(nxt, buf ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();  // all but the newest group: the current row tile has landed
+    bool has_n = false;
+    if (kRowBufs == 2) {
+      has_n = advance(nxt);
+      if (has_n) issue(nxt, buf ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();  // all but the newest group: the current row tile has landed
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();     // (the first time also: K and V of this CTA's keys are in place)
     {
       const Tile<D>& qs_t = row_tiles[2 * buf];
@@ -476,10 +484,16 @@ __global__ void __launch_bounds__(kThreadsM) attn_bwd_dkv_mma_kernel(BwdMmaArgs 
         mm_nn_acc<D>(dk, da, qs_t, c0, lane);
       }
     }
-    __syncthreads();  // this pair of buffers is refilled by the next iteration's copy
+    __syncthreads();  // this pair of buffers is refilled by the next copy
+    if (kRowBufs == 1) {
+      has_n = advance(nxt);
+      if (has_n) issue(nxt, 0);
+      cp_async_commit();
+    } else {
+      buf ^= 1;
+    }
     cur = nxt;
     has = has_n;
-    buf ^= 1;
   }
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) {
@@ -521,7 +535,7 @@ int launch_mma(BwdMmaArgs a, cudaStream_t st) {
     attn_bwd_store_dq_last_kernel<D><<<std::max(blocks, 1), 256, 0, st>>>(a);
     BRK_CUDA(cudaGetLastError());
   }
-  const int smem = 6 * (int)sizeof(Tile<D>) + 4 * kT * (int)sizeof(float);
+  const int smem = (2 + 2 * kRowBufs) * (int)sizeof(Tile<D>) + 2 * kRowBufs * kT * (int)sizeof(float);
   BRK_CUDA(cudaFuncSetAttribute(attn_bwd_dkv_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   // block 0's keys are seen by every row block: many CTAs per key tile; the other blocks' keys by two at most
   a.m_base = 0;
