@@ -25,9 +25,9 @@ namespace {
 constexpr int kT = 64;         // tokens (rows or keys) per staged tile
 constexpr int kWarps = 4;
 constexpr int kThreadsM = kWarps * 32;
-// Row-tile buffers of the dk/dv kernel: 1 = the next tile is requested after the current one has been multiplied
-// (70 KB of shared memory, three CTAs per SM cover the copy), 2 = requested before (104 KB, two CTAs per SM).
-constexpr int kRowBufs = 1;
+// Row-tile buffers of the dk/dv kernel: 2 = the next tile is requested before the current one is multiplied (104 KB
+// of shared memory; the kernel runs two CTAs per SM anyway: it keeps its keys' A fragments in registers), 1 = after.
+constexpr int kRowBufs = 2;
 
 struct BwdMmaArgs {
   View q, k, v, o, d_o, dq;
@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(256) attn_bwd_store_dq_last_kernel(BwdMmaArgs 
 
 // grid: x = 64-key tile of the block, y = key block, z = ((prompt * Nk + KV head) * nsplit + split)
 template <int D>
-__global__ void __launch_bounds__(kThreadsM, 3) attn_bwd_dkv_mma_kernel(BwdMmaArgs a) {
+__global__ void __launch_bounds__(kThreadsM, 2) attn_bwd_dkv_mma_kernel(BwdMmaArgs a) {
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   Tile<D>& ks_t = *reinterpret_cast<Tile<D>*>(dyn_smem);
   Tile<D>& vs_t = *reinterpret_cast<Tile<D>*>(dyn_smem + sizeof(Tile<D>));
@@ -429,6 +429,10 @@ __global__ void __launch_bounds__(kThreadsM, 3) attn_bwd_dkv_mma_kernel(BwdMmaAr
       cp_async4(row_stats + buf * 2 * kT + tid, (tid < kT ? a.lse : a.delta) + rid);
     }
   };
+  __syncthreads();  // K and V of this CTA's keys are in place
+  uint32_t ka_k[D / 16][4], ka_v[D / 16][4];  // this warp's 16 keys as A fragments, for every row tile
+  load_a<D>(ka_k, ks_t, warp * 16, lane);
+  load_a<D>(ka_v, vs_t, warp * 16, lane);
   RowIt cur{split, 0, 0, 0, 0, 0, false};
   bool has = entry_init(cur);
   if (has) issue(cur, 0);
@@ -456,12 +460,9 @@ __global__ void __launch_bounds__(kThreadsM, 3) attn_bwd_dkv_mma_kernel(BwdMmaAr
       // own block: this warp's keys start at token j0 + 16 warp; rows before that see none of them
       const int c_first = own ? max(0, ((j0 + warp * 16 - t0) / 16) * 16) : 0;
       for (int c0 = c_first; c0 < nv; c0 += 16) {
-        uint32_t ka[D / 16][4];
         float st[2][4], dpt[2][4];
-        load_a<D>(ka, ks_t, warp * 16, lane);
-        mm_nt<D>(st, ka, qs_t, c0, lane);   // S^T: rows = keys, columns = query tokens
-        load_a<D>(ka, vs_t, warp * 16, lane);
-        mm_nt<D>(dpt, ka, gs_t, c0, lane);  // dP^T
+        mm_nt<D>(st, ka_k, qs_t, c0, lane);   // S^T: rows = keys, columns = query tokens
+        mm_nt<D>(dpt, ka_v, gs_t, c0, lane);  // dP^T
         float p[2][4], ds[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
