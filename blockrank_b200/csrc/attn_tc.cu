@@ -654,7 +654,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const uint32_t a_lo = (uint32_t)q_desc0, a_hi = (uint32_t)(q_desc0 >> 32);
       const uint32_t b_lo = (uint32_t)k_desc0 + (uint32_t)slot * (kSlotHalf >> 4), b_hi = (uint32_t)(k_desc0 >> 32);
       if (leader) {
-#pragma unroll
+#pragma unroll 1
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t aoff = (uint32_t)(ks >> 2) * ((BM * 128) >> 4) + (uint32_t)(ks & 3) * 2;
           const uint32_t boff = (uint32_t)(ks >> 2) * (kPoolHalf >> 4) + (uint32_t)(ks & 3) * 2;
@@ -669,7 +669,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const uint32_t b_lo = (uint32_t)v_desc0 + (uint32_t)slot * (kSlotHalf >> 4), b_hi = (uint32_t)(v_desc0 >> 32);
       const int ksteps = (keys + 15) >> 4;
       if (leader) {
-#pragma unroll
+#pragma unroll 1
         for (int ks = 0; ks < BT / 16; ++ks)
           if (ks < ksteps)
             ptx::mma_ts_lohi(tm_o, tm_s + (uint32_t)ks * 8, b_lo + (uint32_t)ks * ((16 * 128) >> 4), b_hi, idesc_pv,
@@ -859,11 +859,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ptx::tmem_wait_ld(sr);
           }
           // Visibility.  Slots fully inside the visible region need no masking (the common case).
-          // Ragged tails and the causal diagonal make columns [0, lim) of a row visible; the
-          // 8-column groups below the warp's smallest lim need no masking either, the groups at or
-          // above its largest lim are skipped altogether (their P is zero), and only the groups in
-          // between are masked element by element.  Padded context ranges (reference layout with
-          // gaps between blocks) take the general per-element path.
+          // Ragged tails and the causal diagonal make columns [0, lim) of a row visible; padded
+          // context ranges (reference layout with gaps between blocks) are masked column by column.
+          // A masked logit becomes -inf with one select per column, so that its P is exactly 0 and the
+          // pass below stays one basic block: skipping the 8-column groups that no row of the warp sees
+          // with warp-uniform branches measured 5 % slower over the whole kernel than exponentiating them.
           int lim = BN, lim_lo = BN, lim_hi = BN;
           const bool premasked = !own && ctx_check;  // padded context: columns masked one by one from the slot-validity ballots
           if (nk < BN || (own && own_off + BN - 1 > it.t0) || premasked) {
@@ -883,24 +883,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               lim_hi = __reduce_max_sync(0xffffffffu, lim);
             }
           }
-          // The slot is processed by one of two instantiations: straight-line code when nothing is
-          // masked per group (one basic block: exponentials, polynomial and conversions interleave
-          // freely), or the grouped form with warp-uniform branches around every 8 columns.
-          auto process = [&](auto grouped_tag) {
-            constexpr bool kGrouped = decltype(grouped_tag)::value;
+          if (!(lim_hi == BN && lim_lo == BN) && !premasked) {
+#pragma unroll
+            for (int c = 0; c < 64; ++c) sr[c] = c < lim ? sr[c] : 0xff800000u;  // -inf: P = 0 exactly
+          }
+          {
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 8) {
-              if (!kGrouped || c0 < lim_hi) {
-                if (kGrouped && c0 + 8 > lim_lo) {
-#pragma unroll
-                  for (int c = c0; c < c0 + 8; ++c) sr[c] = (c < lim || premasked) ? sr[c] : 0xff800000u;  // -inf
-                }
-#pragma unroll
-                for (int c = c0; c < c0 + 8; c += 2)
-                  mx4[(c >> 1) & 3] = ptx::max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-              }
-            }
+            for (int c = 0; c < 64; c += 2)
+              mx4[(c >> 1) & 3] = ptx::max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
             float m_new = fmaxf(m_run, mx);
             if (m_run != -INFINITY && m_new - m_run <= kLazy) m_new = m_run;  // keep the old reference: p <= 2^8
@@ -949,10 +940,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ptx::f32x2 ps2[2] = {0ull, 0ull};
             uint32_t pk[32];
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 8) {
-              if (!kGrouped || c0 < lim_hi) {
+            {
+              {
 #pragma unroll
-                for (int c = c0; c < c0 + 8; c += 4) {
+                for (int c = 0; c < 64; c += 4) {
                   const ptx::f32x2 t01 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nr2);
                   const ptx::f32x2 t23 = ptx::fma2(ptx::pack2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nr2);
                   float t0, t1, p2, p3;
@@ -963,7 +954,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                   if ((kPolyOf8 == 4) || (kPolyOf8 == 2 && (c & 4))) {
                     const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
                     ptx::unpack2(p23, p2, p3);
-                    if (kGrouped && c0 + 8 > lim_lo) {
+                    if (lim_lo < BN) {
                       // a masked column must contribute exactly nothing: the polynomial maps -inf to 2^-126,
                       // which times a huge (finite) value in a padding slot of V would still be visible
                       p2 = sr[c + 2] == 0xff800000u ? 0.f : p2;
@@ -981,9 +972,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                   pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h0);
                   pk[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
                 }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) pk[(c0 >> 1) + i] = 0u;
               }
             }
             ptx::tmem_st32(tmem_lane + (uint32_t)h * 32, pk);
@@ -991,8 +979,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ptx::unpack2(ps2[0], s0, s1);
             ptx::unpack2(ps2[1], s2, s3);
             l_run = l_run * corr + ((s0 + s1) + (s2 + s3));
-          };
-          if (lim_hi == BN && lim_lo == BN) process(std::false_type{}); else process(std::true_type{});
+          }
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
