@@ -841,6 +841,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int cnt = min(2, n_mine - 2 * t);  // slots of this tile the chain sees
         wait(kSFull + x, s_seen, 30 + x);
         ++s_seen;
+        if (t > 0) {
+          // The previous tile's P V was issued before this tile's Q K^T, so it has completed too: O is stable
+          // and the P columns (first half of S) may be overwritten.  Consuming that phase here keeps the pass
+          // below free of calls (64 logits are live across its middle).
+          wait(kPVDone + x, pv_seen, 32 + x);
+          ++pv_seen;
+        }
         ptx::tc_fence_after_sync();
         __syncwarp();
         // One pass per 64-key slot: logits -> registers, mask, row maximum, running-max update,
@@ -901,40 +908,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const bool changed = m_new != m_run;
             m_run = m_new;
 
-            if (h == 0 && t > 0) {
-              // previous P V done: O is stable and the P columns (first half of S) may be overwritten
-              wait(kPVDone + x, pv_seen, 32 + x);
-              ++pv_seen;
-              ptx::tc_fence_after_sync();
-            }
-            if ((t > 0 || h > 0) && __any_sync(0xffffffffu, changed)) {
-              // The reference moved by more than the lazy threshold (rare): bring what was accumulated
-              // against the old one in line -- O of the earlier tiles, P of this tile's first slot.
-              if (t > 0) {
-#pragma unroll 1
-                for (int ch = 0; ch < HD / 32; ++ch) {
-                  uint32_t orow[32];
-                  ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-                  ptx::tmem_wait_ld(orow);
-#pragma unroll
-                  for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
-                  ptx::tmem_st32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
-                }
-              }
-              if (h > 0) {
-                uint32_t p0[32];
-                ptx::tmem_ld32(tmem_lane, p0);
-                ptx::tmem_wait_ld(p0);
-                const __nv_bfloat162 c2 = __float2bfloat162_rn(corr);  // corr is 1 or at most 2^-8: exact enough in bf16
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&p0[i]), c2);
-                  p0[i] = *reinterpret_cast<uint32_t*>(&v);
-                }
-                ptx::tmem_st32(tmem_lane, p0);
-              }
-              ptx::tmem_wait_st();
-            }
             // p with packed fp32x2 arithmetic; see kPolyOf8 for where the exponentials are evaluated
             const ptx::f32x2 sc2 = ptx::pack2(a.scale_log2, a.scale_log2), nr2 = ptx::pack2(neg_ref, neg_ref);
             ptx::f32x2 ps2[2] = {0ull, 0ull};
@@ -975,6 +948,36 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               }
             }
             ptx::tmem_st32(tmem_lane + (uint32_t)h * 32, pk);
+            if ((t > 0 || h > 0) && __any_sync(0xffffffffu, changed)) {
+              // The reference moved by more than the lazy threshold (rare): bring what was accumulated
+              // against the old one in line -- O of the earlier tiles, P of this tile's first slot.  (Behind the
+              // exponentials, so that the common path from the row maximum to P is one basic block; all of it
+              // precedes the arrival that lets the MMA warp read P and add to O.)
+              if (t > 0) {
+#pragma unroll 1
+                for (int ch = 0; ch < HD / 32; ++ch) {
+                  uint32_t orow[32];
+                  ptx::tmem_ld32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+                  ptx::tmem_wait_ld(orow);
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
+                  ptx::tmem_st32(tmem_lane + kColO + (uint32_t)ch * 32, orow);
+                }
+              }
+              if (h > 0) {
+                uint32_t p0[32];
+                ptx::tmem_ld32(tmem_lane, p0);
+                ptx::tmem_wait_ld(p0);
+                const __nv_bfloat162 c2 = __float2bfloat162_rn(corr);  // corr is 1 or at most 2^-8: exact enough in bf16
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  __nv_bfloat162 v = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&p0[i]), c2);
+                  p0[i] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                ptx::tmem_st32(tmem_lane, p0);
+              }
+              ptx::tmem_wait_st();
+            }
             float s0, s1, s2, s3;
             ptx::unpack2(ps2[0], s0, s1);
             ptx::unpack2(ps2[1], s2, s3);
