@@ -871,10 +871,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           // A masked logit becomes -inf with one select per column, so that its P is exactly 0 and the
           // pass below stays one basic block: skipping the 8-column groups that no row of the warp sees
           // with warp-uniform branches measured 5 % slower over the whole kernel than exponentiating them.
-          int lim = BN, lim_lo = BN, lim_hi = BN;
           const bool premasked = !own && ctx_check;  // padded context: columns masked one by one from the slot-validity ballots
-          if (nk < BN || (own && own_off + BN - 1 > it.t0) || premasked) {
-            lim = nk;
+          if (nk < BN || (own && own_off + BN - 1 > it.t0) || premasked) {  // (warp-uniform)
+            int lim = nk;
             if (own) lim = max(0, min(nk, tok - own_off + 1));
             if (premasked) {
               const unsigned v0 = __ballot_sync(0xffffffffu, slot_valid(bs, bl, a.M, lo + lane));
@@ -884,15 +883,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 const bool ok = c < lim && (((c < 32 ? v0 : v1) >> (c & 31)) & 1u);
                 sr[c] = ok ? sr[c] : 0xff800000u;  // -inf
               }
-              lim_lo = 0;  // every group takes the masked form below (masked columns get P = 0 exactly)
             } else {
-              lim_lo = __reduce_min_sync(0xffffffffu, lim);
-              lim_hi = __reduce_max_sync(0xffffffffu, lim);
-            }
-          }
-          if (!(lim_hi == BN && lim_lo == BN) && !premasked) {
 #pragma unroll
-            for (int c = 0; c < 64; ++c) sr[c] = c < lim ? sr[c] : 0xff800000u;  // -inf: P = 0 exactly
+              for (int c = 0; c < 64; ++c) sr[c] = c < lim ? sr[c] : 0xff800000u;  // -inf: P = 0 exactly
+            }
           }
           {
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
@@ -927,12 +921,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                   if ((kPolyOf8 == 4) || (kPolyOf8 == 2 && (c & 4))) {
                     const ptx::f32x2 p23 = ptx::ex2_poly2(t23);
                     ptx::unpack2(p23, p2, p3);
-                    if (lim_lo < BN) {
-                      // a masked column must contribute exactly nothing: the polynomial maps -inf to 2^-126,
-                      // which times a huge (finite) value in a padding slot of V would still be visible
-                      p2 = sr[c + 2] == 0xff800000u ? 0.f : p2;
-                      p3 = sr[c + 3] == 0xff800000u ? 0.f : p3;
-                    }
+                    // a masked column must contribute exactly nothing: the polynomial maps -inf to 2^-126,
+                    // which times a huge (finite) value in a padding slot of V would still be visible
+                    p2 = sr[c + 2] == 0xff800000u ? 0.f : p2;
+                    p3 = sr[c + 3] == 0xff800000u ? 0.f : p3;
                   } else {
                     float t2, t3;
                     ptx::unpack2(t23, t2, t3);
