@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(kThreads) attn_bwd_dkv_kernel(BwdArgs a) {
   span_of(a, b, m, start, len);
   const int j0 = blockIdx.x * kRows;
   if (j0 >= len) return;
+  if (split >= ((m == 0) ? a.M : ((m < a.M - 1) ? 2 : 1))) return;  // no row block left for this split
   const int j = j0 + kr;  // key token within the block
   const bool kvalid = j < len;
 
