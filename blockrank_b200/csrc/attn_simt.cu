@@ -46,18 +46,23 @@ __global__ void __launch_bounds__(kThreads) attn_simt_kernel(SimtArgs a) {
   const int start = bs[m], len = bl[m];
 
   T* ob = reinterpret_cast<T*>(a.o.ptr) + (int64_t)b * a.o.sb;
-  if (tile == 0) {
-    // padding slots in front of this block (and behind the last block) are written as zeros
-    const int gap0 = (m == 0) ? 0 : bs[m - 1] + bl[m - 1];
+  {
+    // Padding slots are written as zeros: the gap in front of this block by the block's first CTA, the gap behind
+    // the last block (thousands of rows when a batch is padded to its longest prompt) in slices by all of the
+    // last block's CTAs.
     const int per_row = G * (D / 4);
-    for (int pass = 0; pass < 2; ++pass) {
-      const int lo = pass == 0 ? gap0 : start + len;
-      const int hi = pass == 0 ? start : ((m == a.M - 1) ? a.S : start + len);
+    auto zero_rows = [&](int lo, int hi) {
       for (int i = tid; i < (hi - lo) * per_row; i += kThreads) {
         const int s = lo + i / per_row, rem = i % per_row;
         const int h = g * G + rem / (D / 4), d4 = rem % (D / 4);
         store4(ob + (int64_t)s * a.o.ss + (int64_t)h * a.o.sh + d4 * 4, make_float4(0.f, 0.f, 0.f, 0.f));
       }
+    };
+    if (tile == 0) zero_rows((m == 0) ? 0 : bs[m - 1] + bl[m - 1], start);
+    if (m == a.M - 1) {
+      const int lo = start + len, rows = a.S - lo;
+      const int per = (rows + (int)gridDim.x - 1) / (int)gridDim.x;
+      if (rows > 0) zero_rows(lo + min(rows, tile * per), lo + min(rows, (tile + 1) * per));
     }
   }
   const int t0 = tile * TQ;

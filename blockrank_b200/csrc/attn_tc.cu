@@ -349,18 +349,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int G = a.G;
 
   // ---- padding slots of the output are written as zeros (gaps in front of / behind blocks) ----
-  for (int gi = blockIdx.x; gi < a.B * (a.M + 1); gi += gridDim.x) {
-    const int b = gi / (a.M + 1), m = gi % (a.M + 1);
-    const int32_t* bs = a.blk_start + (size_t)b * a.M;
-    const int32_t* bl = a.blk_len + (size_t)b * a.M;
-    const int lo = (m == 0) ? 0 : bs[m - 1] + bl[m - 1];
-    const int hi = (m == a.M) ? a.S : bs[m];
-    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.sb;
+  {
     const int per_row = a.N * (HD / 8);
-    for (int i = tid; i < (hi - lo) * per_row; i += kThreads) {
-      const int s = lo + i / per_row, rem = i % per_row;
-      *reinterpret_cast<uint4*>(ob + (int64_t)s * a.o.ss + (int64_t)(rem / (HD / 8)) * a.o.sh + (rem % (HD / 8)) * 8) =
-          make_uint4(0, 0, 0, 0);
+    auto zero_rows = [&](int b, int lo, int hi) {
+      __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.o.ptr) + (int64_t)b * a.o.sb;
+      for (int i = tid; i < (hi - lo) * per_row; i += kThreads) {
+        const int s = lo + i / per_row, rem = i % per_row;
+        *reinterpret_cast<uint4*>(ob + (int64_t)s * a.o.ss + (int64_t)(rem / (HD / 8)) * a.o.sh + (rem % (HD / 8)) * 8) =
+            make_uint4(0, 0, 0, 0);
+      }
+    };
+    // the gap in front of a block (at most a block's padding): one CTA each
+    for (int gi = blockIdx.x; gi < a.B * a.M; gi += gridDim.x) {
+      const int b = gi / a.M, m = gi % a.M;
+      const int32_t* bs = a.blk_start + (size_t)b * a.M;
+      const int32_t* bl = a.blk_len + (size_t)b * a.M;
+      zero_rows(b, (m == 0) ? 0 : bs[m - 1] + bl[m - 1], bs[m]);
+    }
+    // The gap behind the last block holds thousands of rows when a batch is padded to its longest prompt (one
+    // CTA writing all of it took longer than the rest of the kernel): every CTA takes a slice of it.
+    for (int b = 0; b < a.B; ++b) {
+      const int lo = a.blk_start[(size_t)b * a.M + a.M - 1] + a.blk_len[(size_t)b * a.M + a.M - 1];
+      const int rows = a.S - lo;
+      if (rows <= 0) continue;
+      const int per = (rows + (int)gridDim.x - 1) / (int)gridDim.x;
+      const int slot = (int)((blockIdx.x + (unsigned)b) % gridDim.x);
+      zero_rows(b, lo + min(rows, slot * per), lo + min(rows, (slot + 1) * per));
     }
   }
 

@@ -114,6 +114,31 @@ def test_many_blocks_grouped_with_resident_prefix():
     assert (o_tc.float() - o_si.float())[:, :T].abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("algo", [SIMT, TC])
+def test_long_gap_behind_the_last_block_is_zeroed(algo):
+    """A batch padded to its longest prompt: the thousands of rows behind the short prompt's last block are zeroed in
+    slices by many CTAs.  Every padding row must come back exactly zero (the output starts as NaN) and every valid
+    row must agree with what the same prompt gives when it is run alone in a tight buffer."""
+    bls = [[64] + [24] * 40 + [48], [64] + [160] * 40 + [48]]
+    start, ln, S, mbl = H_.packed_spans(bls)
+    g = torch.Generator(device="cuda").manual_seed(21)
+    mk = lambda h: (torch.randn(2, S, h, D, generator=g, device="cuda") * 0.5).bfloat16().transpose(1, 2)
+    q, k, v = mk(N), mk(NK), mk(NK)
+    out = torch.full((2, S, N, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.attention(q, k, v, start.cuda(), ln.cuda(), D ** -0.5, mbl, out=out, algo=algo, max_query_len=48)
+    ops.check_status()
+    for b, bl in enumerate(bls):
+        T = sum(bl)
+        assert T < S or b == 1
+        assert out[b, T:].float().abs().max().item() == 0 if T < S else True   # NaN would fail the comparison too
+        st1, ln1, S1, mbl1 = H_.packed_spans([bl])
+        solo = ops.attention(q[b:b + 1, :, :S1], k[b:b + 1, :, :S1], v[b:b + 1, :, :S1], st1.cuda(), ln1.cuda(), D ** -0.5,
+                             mbl, algo=algo, max_query_len=48)
+        ops.check_status()
+        # (the query block's key chunks depend on the buffer length, so its rows may differ in the last bf16 bit)
+        assert (out[b, :T].float() - solo[0, :T].float()).abs().max().item() < 1e-2
+
+
 def test_large_finite_values_in_padding_slots_do_not_leak():
     """Keys outside a row's visible set get probability exactly zero, so finite garbage in the padding slots of
     K/V (here 1e30 behind every block of a padded grid) cannot reach a valid output row."""
