@@ -458,12 +458,16 @@ def run_ours(args, cfg):
     mbl, mql = host["max_block_len"], max(bl[-1] for bl in bls)
     n_local = len(bls)
     micro = max(1, min(args.micro, n_local))
+    # every forward is padded to the longest prompt of ITS micro-batch, as a caller batching ragged prompts would do
+    # (the collated batch is padded to the longest local prompt)
+    s_mb = {i: min(host["input_ids"].shape[1], -(-max(sum(bl) for bl in bls[i:i + micro]) // 8) * 8)
+            for i in range(0, n_local, micro)}
 
     def step_resident():
         outs = []
         for i in range(0, n_local, micro):
             sl = slice(i, i + micro)
-            lg, _ = rk.score(devb["input_ids"][sl], devb["position_ids"][sl], devb["block_spans"][0, sl],
+            lg, _ = rk.score(devb["input_ids"][sl, :s_mb[i]], devb["position_ids"][sl, :s_mb[i]], devb["block_spans"][0, sl],
                              devb["block_spans"][1, sl], mbl, devb["signal_rows"][sl], mql)
             outs.append(lg)
         scores = torch.cat(outs)
@@ -473,7 +477,7 @@ def run_ours(args, cfg):
         outs = []
         for i in range(0, n_local, micro):
             sl = slice(i, i + micro)
-            mb = {"input_ids": host["input_ids"][sl], "position_ids": host["position_ids"][sl],
+            mb = {"input_ids": host["input_ids"][sl, :s_mb[i]], "position_ids": host["position_ids"][sl, :s_mb[i]],
                   "block_spans": host["block_spans"][:, sl], "signal_rows": host["signal_rows"][sl],
                   "max_block_len": mbl}
             outs.append(rk.rank_host(mb))
@@ -524,8 +528,7 @@ def run_ours(args, cfg):
             dist.destroy_process_group()
         return
     pk = peaks()
-    S = host["input_ids"].shape[1]
-    work = [attention_work(bl, S) for bl in bls]
+    work = [attention_work(bl, s_mb[(j // micro) * micro]) for j, bl in enumerate(bls)]
     step_exact, step_bytes, step_tile = (sum(w[i] for w in work) for i in range(3))
     # every timed attention launch covers one micro-batch of one layer: per step, SCORE_LAYER launches per micro-batch
     attn_s_per_step = sum(attn_ms) / 1e3 / args.steps / SCORE_LAYER      # all micro-batches of one layer
@@ -536,7 +539,8 @@ def run_ours(args, cfg):
     sc_bytes = sum(score_bytes(bl) for bl in bls)
     value = total * args.steps / (total_ms / 1e3)
     e2e = total * args.steps / (e2e_ms / 1e3)
-    h2d = sum(v.numel() * v.element_size() for v in host.values() if torch.is_tensor(v))
+    h2d = sum(v.numel() * v.element_size() for key, v in host.items() if torch.is_tensor(v) and key not in ("input_ids", "position_ids"))
+    h2d += sum(2 * 8 * len(bls[i:i + micro]) * s for i, s in s_mb.items())  # int64 ids and positions of each forward
     nd = cfg["docs"]
     d2h = n_local * nd * 4 + n_local * min(10, nd) * 8
     tc = args.algo != "simt"
